@@ -1,0 +1,225 @@
+"""Pin the CPU oracle: bit-for-bit against the reference's golden vectors, and
+against the live reference where a checkout is reachable."""
+
+from __future__ import annotations
+
+import sys
+
+import pytest
+import torch
+
+from conftest import load_golden, reference_root
+from oracle import gdn_oracle as orc
+
+torch.set_num_threads(1)   # same reduction order as the fixture generator
+
+
+def test_quantizers_match_golden():
+    g = load_golden("quantizers")
+    x = g["x"]
+    for bits in (3, 4, 5, 6, 8):
+        codes, scale, deq = orc.quantize_per_column(x, bits)
+        assert torch.equal(codes, g[f"pv_codes_{bits}"])
+        assert torch.equal(scale, g[f"pv_scale_{bits}"])
+        assert torch.equal(deq, g[f"pv_deq_{bits}"])
+        assert torch.equal(deq, g[f"axis_m2_{bits}"])          # quant.py per_axis(dim=-2)
+        _, hs, hdeq = orc.quantize_per_head(x, bits)
+        assert torch.equal(hdeq, g[f"uni_deq_{bits}"])
+        assert torch.equal(hs, g[f"uni_scale_{bits}"][..., 0, 0])
+    # per-head residual quantizer (modal_residual.py:51-55)
+    e = x * 1e-3
+    for prec, fmt in (("int8", orc.RES_INT8), ("int4", orc.RES_INT4)):
+        stored, scale = orc.quant_residual_kv(e, fmt, resid_scale="head")
+        deq = orc.dequant_residual_kv(stored, scale, fmt)
+        assert torch.equal(deq, g[f"resid_head_{prec}"])
+
+
+def test_scale_floor_column_is_zero_codes():
+    g = load_golden("quantizers")
+    codes, scale, _ = orc.quantize_per_column(g["x"], 8)
+    assert torch.all(codes[0, :, 3] == 0)
+    assert scale[0, 3].item() == pytest.approx(1e-12 / 127, rel=1e-6)
+    # the slot path floors the scale itself (quantized_packed_decode.py:206)
+    _, s2, _ = orc.quantize_per_column(g["x"], 8, eps_mode=orc.EPS_ON_SCALE)
+    assert s2[0, 3].item() == pytest.approx(1e-12, rel=1e-6)
+
+
+def test_recurrence_matches_golden():
+    g = load_golden("recurrence")
+    o, h = orc.gdn_decode(g["h0"][0], g["q"][:, 0], g["k"][:, 0], g["v"][:, 0],
+                          g["alpha"][:, 0], g["beta"][:, 0])
+    assert torch.equal(o, g["o"]) and torch.equal(h, g["h_final"])
+    hb, ob = orc.gdn_step(g["h0"], g["q"][0], g["k"][0], g["v"][0], g["alpha"][0], g["beta"][0])
+    assert torch.equal(hb, g["h_step_b"]) and torch.equal(ob, g["o_step_b"])
+
+
+@pytest.mark.parametrize("tag,bits", [("small", 8), ("small", 4), ("tile128", 8)])
+@pytest.mark.parametrize("res_fmt", [orc.RES_FP32, orc.RES_FP16, orc.RES_FP8, orc.RES_INT8])
+def test_fused_step_matches_golden(tag, bits, res_fmt):
+    fp8 = ("e0", "e1", "e2") if res_fmt == orc.RES_FP8 else ()
+    g = load_golden(f"step_{tag}_fmt{res_fmt}_b{bits}", fp8_keys=fp8)
+    st = orc.init_quant_state(g["h0"], bits, res_fmt)
+    for t in range(3):
+        o, codes, scale, e, es = orc.quant_step(
+            *st, g["q"][t], g["k"][t], g["v"][t], g["alpha"][t], g["beta"][t], bits, res_fmt)
+        assert torch.equal(o, g[f"o{t}"])
+        assert torch.equal(codes, g[f"codes{t}"])
+        assert torch.equal(scale, g[f"scale{t}"])
+        if res_fmt == orc.RES_FP8:
+            assert torch.equal(e.view(torch.uint8), g[f"e{t}"].view(torch.uint8))
+        else:
+            assert torch.equal(e, g[f"e{t}"])
+        if res_fmt == orc.RES_INT8:
+            assert torch.equal(es, g[f"es{t}"])
+        else:
+            assert es is None
+        st = (codes, scale, e, es)
+
+
+def test_chained_decode_matches_golden():
+    g = load_golden("decode_oracle")
+    h0 = g["h0"]
+    _, _, deq0 = orc.quantize_per_column(h0, 8)
+    h = deq0[0].clone()
+    e = torch.zeros_like(h)
+    outs = []
+    for t in range(g["q"].shape[0]):
+        h, o = orc.gdn_step(h, g["q"][t, 0], g["k"][t, 0], g["v"][t, 0],
+                            g["alpha"][t, 0], g["beta"][t, 0])
+        h, e = orc.error_feedback(h, e, lambda x: orc.quantize_per_column(x, 8)[2])
+        outs.append(o)
+    assert torch.equal(torch.stack(outs), g["o"])
+    assert torch.equal(h, g["h_final"]) and torch.equal(e, g["e_final"])
+
+
+def test_mechanism_arms_match_golden():
+    g = load_golden("mechanism")
+    args = (g["h0"], g["q"], g["k"], g["v"], g["alpha"], g["beta"])
+    _, h_ref = orc.gdn_decode(*args)
+    assert torch.equal(h_ref, g["h_ref"])
+    for bits in (3, 4, 8):
+        assert torch.equal(orc.chained_ef_decode(*args, bits, "head", False), g[f"head_noef_{bits}"])
+        assert torch.equal(orc.chained_ef_decode(*args, bits, "head", True), g[f"head_ef_{bits}"])
+        assert torch.equal(orc.chained_ef_decode(*args, bits, "column", True), g[f"col_ef_{bits}"])
+    # error feedback helps at every bit width (the reference's headline mechanism)
+    rel = lambda x: ((x - h_ref).norm() / h_ref.norm()).item()
+    for bits in (3, 4, 8):
+        assert rel(g[f"head_ef_{bits}"]) < rel(g[f"head_noef_{bits}"])
+
+
+def test_rounding_ties_match_golden():
+    g = load_golden("ties_kv")
+    K, V = g["target"].shape
+    z = lambda *s: torch.zeros(*s)
+    o, codes, scale, e, _ = orc.quant_step(
+        torch.zeros(1, 1, K, V, dtype=torch.int8), torch.ones(1, 1, V),
+        g["target"][None, None].contiguous(), None, z(1, 1, K), z(1, 1, K), z(1, 1, V),
+        z(1, 1), z(1, 1), 8, orc.RES_FP32)
+    assert torch.equal(codes, g["codes"]) and torch.equal(codes[0, 0].float(), g["expected"])
+    ratios = g["target"].abs()
+    assert int(((ratios % 1.0) == 0.5).sum()) > 0          # not vacuous
+    naive = torch.floor(g["target"] + 0.5).clamp(-127, 127)
+    assert int((naive != g["expected"]).sum()) > 0          # discriminates floor(x + .5)
+
+
+def test_slot_path_helpers_match_golden():
+    g = load_golden("slot_path")
+    B, H, HV, K, V = 3, 2, 4, 32, 16
+    sc, ss, rc, rs = orc.init_quantized_pool(5, HV, V, K, h0=g["pool"])
+    assert torch.equal(sc, g["codes8"]) and torch.equal(ss, g["scale8"])
+    assert list(rc.shape) == g["rc8_shape"].tolist()
+    rc4 = orc.init_quantized_pool(5, HV, V, K, h0=g["pool"], resid_fmt=orc.RESID_INT4)[2]
+    assert list(rc4.shape) == g["rc4_shape"].tolist()
+    assert [orc.state_bytes_per_slot(32, 128, 128, False, 4),
+            orc.state_bytes_per_slot(32, 128, 128, False, 2),
+            orc.state_bytes_per_slot(32, 128, 128, True, resid_fmt=orc.RESID_INT8),
+            orc.state_bytes_per_slot(32, 128, 128, True, resid_fmt=orc.RESID_INT4)] == g["bytes"].tolist()
+
+    q, k, v = orc.unpack_mixed_qkv(g["mixed0"], H, HV, K, V, K ** -0.5, True)
+    assert torch.equal(q, g["q0"]) and torch.equal(k, g["k0"]) and torch.equal(v, g["v0"])
+    alpha, beta = orc.gates(g["a0"], g["b0"], g["A_log0"], g["dt_bias0"])
+    # the reference's test helper uses log1p(exp(x)); the kernel (which the
+    # oracle follows) uses log(1 + exp(x)): equal to fp32 rounding noise
+    torch.testing.assert_close(alpha, g["alpha0"], rtol=1e-6, atol=1e-7)
+    assert torch.equal(beta, g["beta0"])
+
+
+def test_slot_path_tracks_reference_vk_oracle():
+    """The slot step with an int8 (then int4) residual must stay at the
+    quantization noise floor of the reference's fp32-residual [V, K] oracle,
+    at the bounds the reference asserts (test_quantized_packed_decode.py:149-150,
+    353-354)."""
+    g = load_golden("slot_path")
+    H, HV, K, V = 2, 4, 32, 16
+    rel = lambda x, y: ((x - y).norm() / (y.norm() + 1e-12)).item()
+    for fmt, scale_mode, bound in ((orc.RESID_INT8, "v", 5e-2), (orc.RESID_INT4, "v", 8e-2),
+                                   (orc.RESID_INT8, "head", 5e-2), (orc.RESID_INT4, "head", 8e-2)):
+        sc, ss, rc, rs = orc.init_quantized_pool(5, HV, V, K, h0=g["pool"], resid_fmt=fmt,
+                                                 resid_scale=scale_mode)
+        idx = torch.tensor([1], dtype=torch.int32)
+        out = torch.empty(1, 1, HV, V)
+        outs = []
+        for t in range(8):
+            orc.packed_decode_step(g[f"mixed{t}"], g[f"a{t}"], g[f"b{t}"], g[f"A_log{t}"],
+                                   g[f"dt_bias{t}"], K ** -0.5, sc, ss, rc, rs, out, idx,
+                                   use_qk_l2norm_in_kernel=True, resid_fmt=fmt)
+            outs.append(out[0, 0].clone())
+        assert rel(torch.stack(outs), g["o_ref"]) < bound
+        assert rel(orc.dequant_pool_state(sc[1], ss[1]), g["h_ref"]) < bound
+
+
+def test_int4_pack_roundtrip():
+    codes = torch.arange(-8, 8, dtype=torch.int32).repeat(4).reshape(2, 32)
+    packed = orc.pack_int4(codes)
+    assert packed.dtype == torch.int8 and packed.shape == (2, 16)
+    assert torch.equal(orc.unpack_int4(packed), codes)
+    # even index in the low nibble (quantized_packed_decode.py:197)
+    assert int(packed[0, 0]) & 0xF == (-8) & 0xF and (int(packed[0, 0]) >> 4) & 0xF == (-7) & 0xF
+
+
+def test_slot_null_and_isolation():
+    g = load_golden("slot_path")
+    H, HV, K, V = 2, 4, 32, 16
+    pool = g["pool"]
+    mixed = torch.cat([g["mixed0"], g["mixed1"]]); a = torch.cat([g["a0"], g["a1"]])
+    b = torch.cat([g["b0"], g["b1"]])
+    sc, ss, rc, rs = orc.init_quantized_pool(5, HV, V, K, h0=pool)
+    before = sc.clone()
+    out = torch.full((2, 1, HV, V), float("nan"))
+    orc.packed_decode_step(mixed, a, b, g["A_log0"], g["dt_bias0"], K ** -0.5, sc, ss, rc, rs, out,
+                           torch.tensor([3, 0], dtype=torch.int32))
+    assert torch.all(out[1] == 0) and not torch.isnan(out[0]).any()
+    for slot in (0, 1, 2, 4):
+        assert torch.equal(sc[slot], before[slot])
+    assert not torch.equal(sc[3], before[3])
+
+
+@pytest.mark.skipif(reference_root() is None, reason="no reference checkout reachable")
+def test_oracle_equals_live_reference():
+    """Bit-for-bit against the imported reference on a fresh seed (beyond the
+    committed fixtures)."""
+    root = reference_root()
+    sys.path.insert(0, root)
+    try:
+        from statequant import kernel as tk
+    finally:
+        sys.path.remove(root)
+    torch.manual_seed(77)
+    B, HV, K, V = 2, 2, 64, 48
+    h0 = torch.randn(B, HV, K, V) * 0.2
+    for res_fmt in (orc.RES_FP32, orc.RES_FP16, orc.RES_FP8, orc.RES_INT8):
+        st_r = tk.init_quant_state(h0, 8, res_fmt)
+        st_o = orc.init_quant_state(h0, 8, res_fmt)
+        for t in range(4):
+            q = torch.randn(B, HV, K); k = torch.nn.functional.normalize(torch.randn(B, HV, K), dim=-1)
+            v = torch.randn(B, HV, V); alpha = torch.rand(B, HV) * 0.1 + 0.9; beta = torch.rand(B, HV)
+            r = tk.gdn_quant_step_torch(*st_r, q, k, v, alpha, beta, 8, res_fmt)
+            o = orc.quant_step(*st_o, q, k, v, alpha, beta, 8, res_fmt)
+            for x, y in zip(r, o):
+                if x is None:
+                    assert y is None
+                elif x.dtype == torch.float8_e5m2:
+                    assert torch.equal(x.view(torch.uint8), y.view(torch.uint8))
+                else:
+                    assert torch.equal(x, y)
+            st_r, st_o = r[1:], o[1:]
