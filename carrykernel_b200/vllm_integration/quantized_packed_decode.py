@@ -1,0 +1,184 @@
+"""Slot-indexed INT8 + error-feedback decode step in vLLM's GDN state layout.
+
+Same call contract as carrykernel's
+``vllm_integration/quantized_packed_decode.py:242-369`` (itself shaped on
+vLLM's ``fused_recurrent_gated_delta_rule_packed_decode`` with the state tensor
+replaced by four quantized tensors):
+
+* pool ``state_codes [slots, HV, V, K]`` int8 (K contiguous),
+  ``state_scale [slots, HV, V]`` fp32, ``resid_codes [slots, HV, V, K]`` int8
+  (or ``[.., K // 2]`` packed int4: even K in the low nibble),
+  ``resid_scale [slots, HV, V]`` fp32;
+* ``mixed_qkv [B, 2*H*K + HV*V]`` = q | k | v, gates ``a, b [B, HV]``,
+  ``A_log, dt_bias [HV]``, ``out [B, 1, HV, V]`` pre-allocated;
+* request ``n`` updates slot ``ssm_state_indices[n]`` **in place**; a slot id
+  ``<= 0`` (:data:`NULL_BLOCK_ID` padding) writes zeros to ``out[n]`` and leaves
+  the pool alone.  Two requests must not name the same slot.
+
+Additive: ``resid_scale`` may be ``[slots, HV]`` -- one residual scale per
+head instead of one per V-row; the granularity is read off the shape.
+
+The call allocates nothing, never synchronises and reads nothing back to the
+host, so it can be captured in a CUDA graph.  There is no CPU path.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import _lib
+from .._lib import CudaUnavailable  # noqa: F401
+
+QMAX_INT8 = 127.0
+QMAX_INT4 = 7.0
+EPS = 1e-12
+SOFTPLUS_THRESHOLD = 20.0
+NULL_BLOCK_ID = 0
+
+RESID_INT8 = 0
+RESID_INT4 = 1
+
+_RES_ID = {RESID_INT8: _lib.RES_INT8, RESID_INT4: _lib.RES_INT4}
+
+
+def quantized_gated_delta_rule_packed_decode(
+    mixed_qkv: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    A_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    scale: float,
+    state_codes: torch.Tensor,
+    state_scale: torch.Tensor,
+    resid_codes: torch.Tensor,
+    resid_scale: torch.Tensor,
+    out: torch.Tensor,
+    ssm_state_indices: torch.Tensor,
+    use_qk_l2norm_in_kernel: bool = False,
+    resid_fmt: int = RESID_INT8,
+):
+    """Advance every request's slot by one token, in place; returns ``out``."""
+    if mixed_qkv.dim() != 2:
+        raise ValueError(f"mixed_qkv must be 2-D, got {tuple(mixed_qkv.shape)}")
+    if mixed_qkv.stride(-1) != 1:
+        raise ValueError("mixed_qkv must be contiguous in its last dimension")
+    if state_codes.dim() != 4:
+        raise ValueError(f"state_codes must be 4-D, got {tuple(state_codes.shape)}")
+    if state_codes.stride(-1) != 1:
+        raise ValueError("state_codes must be contiguous in its last dimension")
+    if state_codes.dtype != torch.int8 or resid_codes.dtype != torch.int8:
+        raise ValueError("state_codes and resid_codes must be int8 storage")
+    if resid_fmt not in _RES_ID:
+        raise ValueError(f"unknown residual format {resid_fmt}")
+    if resid_fmt == RESID_INT4 and resid_codes.shape[-1] * 2 != state_codes.shape[-1]:
+        raise ValueError(
+            "int4 residual must be packed two codes per byte: expected last dim "
+            f"{state_codes.shape[-1] // 2}, got {resid_codes.shape[-1]}")
+    if resid_fmt == RESID_INT8 and resid_codes.shape != state_codes.shape:
+        raise ValueError("int8 residual must have the same shape as the state")
+    if ssm_state_indices.dim() != 1:
+        raise ValueError("ssm_state_indices must be 1-D")
+    if ssm_state_indices.dtype != torch.int32:
+        raise ValueError("ssm_state_indices must be int32")
+
+    B = mixed_qkv.shape[0]
+    num_slots, HV, V, K = state_codes.shape
+    if out.shape != (B, 1, HV, V):
+        raise ValueError(f"out must be {(B, 1, HV, V)}, got {tuple(out.shape)}")
+    if not out.is_contiguous():
+        raise ValueError("out must be contiguous")
+
+    qkv_dim = mixed_qkv.shape[1]
+    qk_dim = qkv_dim - HV * V
+    if qk_dim <= 0 or qk_dim % 2 != 0:
+        raise ValueError(f"cannot infer H from mixed_qkv width {qkv_dim}")
+    H = (qk_dim // 2) // K
+    if H <= 0 or HV % H != 0 or 2 * H * K != qk_dim:
+        raise ValueError(f"cannot infer H from mixed_qkv width {qkv_dim}")
+    if resid_fmt == RESID_INT4 and K % 2 != 0:
+        raise ValueError(f"int4 residual packing needs an even K, got {K}")
+
+    _lib.require_cuda(state_codes, "state_codes")
+    if resid_scale.dim() == 3:
+        rmode = _lib.SCALE_PER_V
+    elif resid_scale.dim() == 2:
+        rmode = _lib.SCALE_PER_HEAD
+    else:
+        raise ValueError(f"resid_scale must be [slots, HV, V] or [slots, HV], got {tuple(resid_scale.shape)}")
+    # the tile interior of the pool tensors must be dense; only the slot stride is free
+    rk = resid_codes.shape[-1]
+    if state_codes.stride()[1:] != (V * K, K, 1) or resid_codes.stride()[1:] != (V * rk, rk, 1):
+        raise ValueError("pool tensors must be dense within a slot (only the slot stride may vary)")
+    if state_scale.stride()[1:] != (V, 1) or state_scale.dtype != torch.float32:
+        raise ValueError("state_scale must be fp32 [slots, HV, V], dense within a slot")
+    want = (V, 1) if rmode == _lib.SCALE_PER_V else (1,)
+    if resid_scale.stride()[1:] != want or resid_scale.dtype != torch.float32:
+        raise ValueError("resid_scale must be fp32 and dense within a slot")
+    if a.stride(-1) != 1 or b.stride(-1) != 1 or a.dtype != b.dtype:
+        raise ValueError("a and b must share a dtype and be contiguous in their last dimension")
+    A_log = A_log.contiguous()
+    dt_bias = dt_bias.contiguous()
+
+    args = _lib.PackedArgs()
+    args.mixed_qkv, args.stride_mixed_tok, args.qkv_dtype = mixed_qkv.data_ptr(), mixed_qkv.stride(0), _lib.dtype_id(mixed_qkv)
+    args.a, args.stride_a_tok = a.data_ptr(), a.stride(0)
+    args.b, args.stride_b_tok = b.data_ptr(), b.stride(0)
+    args.ab_dtype = _lib.dtype_id(a)
+    args.A_log, args.A_log_dtype = A_log.data_ptr(), _lib.dtype_id(A_log)
+    args.dt_bias, args.dt_bias_dtype = dt_bias.data_ptr(), _lib.dtype_id(dt_bias)
+    args.scale = float(scale)
+    args.state_codes, args.state_scale = state_codes.data_ptr(), state_scale.data_ptr()
+    args.resid_codes, args.resid_scale = resid_codes.data_ptr(), resid_scale.data_ptr()
+    args.stride_state_slot, args.stride_resid_slot = state_codes.stride(0), resid_codes.stride(0)
+    args.stride_sscale_slot, args.stride_rscale_slot = state_scale.stride(0), resid_scale.stride(0)
+    args.out, args.out_dtype = out.data_ptr(), _lib.dtype_id(out)
+    args.ssm_state_indices, args.stride_indices = ssm_state_indices.data_ptr(), ssm_state_indices.stride(0)
+    args.B, args.H, args.HV, args.K, args.V = B, H, HV, K, V
+    args.num_slots = num_slots
+    args.use_qk_l2norm = int(bool(use_qk_l2norm_in_kernel))
+    args.res_fmt = _RES_ID[resid_fmt]
+    args.resid_scale_mode = rmode
+    args.eps_mode = _lib.EPS_ON_SCALE
+    args.qmax = QMAX_INT8
+    args.status = None
+    lib = _lib.load_library()
+    dev = state_codes.device
+    with torch.cuda.device(dev):
+        rc = lib.carry_gdn_packed_decode(args, _lib.current_stream_ptr(dev))
+    _lib.check(rc, "carry_gdn_packed_decode")
+    return out
+
+
+def init_quantized_state(num_slots: int, HV: int, V: int, K: int, device,
+                         h0: torch.Tensor | None = None,
+                         resid_fmt: int = RESID_INT8, resid_scale: str = "v"):
+    """Allocate the quantized pool, optionally seeded from fp32
+    ``h0 [num_slots, HV, V, K]``; the residual starts at zero.  Returns
+    ``(state_codes, state_scale, resid_codes, resid_scale)``.
+    ``resid_scale="head"`` allocates one residual scale per head."""
+    if resid_scale not in ("v", "head"):
+        raise ValueError(f"resid_scale must be 'v' or 'head', got {resid_scale!r}")
+    resid_k = K // 2 if resid_fmt == RESID_INT4 else K
+    state_codes = torch.zeros((num_slots, HV, V, K), dtype=torch.int8, device=device)
+    state_scale = torch.zeros((num_slots, HV, V), dtype=torch.float32, device=device)
+    resid_codes = torch.zeros((num_slots, HV, V, resid_k), dtype=torch.int8, device=device)
+    rs_shape = (num_slots, HV, V) if resid_scale == "v" else (num_slots, HV)
+    resid_scale_t = torch.zeros(rs_shape, dtype=torch.float32, device=device)
+    if h0 is not None:
+        s = h0.abs().amax(dim=-1).clamp(min=EPS) / QMAX_INT8
+        codes = torch.round(h0 / s[..., None]).clamp(-QMAX_INT8, QMAX_INT8)
+        state_codes.copy_(codes.to(torch.int8))
+        state_scale.copy_(s)
+    return state_codes, state_scale, resid_codes, resid_scale_t
+
+
+def state_bytes_per_slot(HV: int, V: int, K: int, quantized: bool,
+                         base_dtype_size: int = 4, resid_fmt: int = RESID_INT8,
+                         resid_scale: str = "v"):
+    """Bytes of recurrent state per request slot (what a cache page must hold)."""
+    if not quantized:
+        return HV * V * K * base_dtype_size
+    codes = HV * V * K
+    resid = HV * V * (K // 2 if resid_fmt == RESID_INT4 else K)
+    scales = HV * V * 4 + (HV * V * 4 if resid_scale == "v" else HV * 4)
+    return codes + resid + scales

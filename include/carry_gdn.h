@@ -1,0 +1,183 @@
+/*
+ * carry_gdn.h -- C ABI of libcarry_gdn.so: the fused Gated-DeltaNet decode step
+ * on an INT8 recurrent state with an error-feedback residual, for NVIDIA B200
+ * (sm_100a).
+ *
+ * Every entry point takes plain device pointers and sizes and a CUDA stream
+ * handle (a cudaStream_t passed as void*).  The library never allocates device
+ * memory, never synchronises and never changes the current device: the caller
+ * makes the right device current, owns every buffer and keeps it alive until
+ * the stream has run the kernel.  Return value: 0 on success, a negative
+ * CARRY_GDN_ERR_* otherwise; nothing throws across this boundary.
+ *
+ * What each entry point replaces in tomalmog/carrykernel (paths relative to
+ * that project) is cited above it.
+ */
+#ifndef CARRY_GDN_H_
+#define CARRY_GDN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define CARRY_GDN_ABI_VERSION 1
+
+/* element types of activations / outputs */
+enum { CARRY_F32 = 0, CARRY_BF16 = 1, CARRY_F16 = 2 };
+
+/* residual storage: ids 0..3 are statequant/kernel.py:59-63; 4 and 5 are new */
+enum {
+  CARRY_RES_FP32 = 0,
+  CARRY_RES_FP16 = 1,
+  CARRY_RES_FP8 = 2,  /* e5m2 */
+  CARRY_RES_INT8 = 3, /* codes + scale */
+  CARRY_RES_INT4 = 4, /* two codes per byte along the contiguous axis, even index low nibble */
+  CARRY_RES_NONE = 5  /* no error feedback: plain re-quantisation */
+};
+
+/* granularity of a scale: one per V channel, or one per (slot, head) matrix */
+enum { CARRY_SCALE_PER_V = 0, CARRY_SCALE_PER_HEAD = 1 };
+
+/* scale floor: max(amax, 1e-12)/qmax (statequant/kernel.py:110,173) or
+ * max(amax/qmax, 1e-12) (vllm_integration/quantized_packed_decode.py:206,213) */
+enum { CARRY_EPS_ON_AMAX = 0, CARRY_EPS_ON_SCALE = 1 };
+
+enum {
+  CARRY_GDN_OK = 0,
+  CARRY_GDN_ERR_NULL = -1,        /* a required pointer is NULL */
+  CARRY_GDN_ERR_SHAPE = -2,       /* a dimension is non-positive or inconsistent */
+  CARRY_GDN_ERR_DTYPE = -3,       /* unknown element type id */
+  CARRY_GDN_ERR_FORMAT = -4,      /* unknown residual format / scale mode, or odd length for int4 */
+  CARRY_GDN_ERR_UNSUPPORTED = -5, /* tile too large for one SM's shared memory */
+  CARRY_GDN_ERR_LAUNCH = -6,      /* the CUDA runtime refused the launch */
+  CARRY_GDN_ERR_NO_DEVICE = -7,   /* no usable sm_100 device is current */
+  CARRY_GDN_ERR_TOO_LARGE = -8    /* beyond a stated fixed capacity */
+};
+
+/* bits of the optional device-side status word (OR-ed in by the kernels) */
+enum {
+  CARRY_GDN_STATUS_BAD_SLOT = 1,   /* a slot id was >= num_slots; that request was treated as padding */
+  CARRY_GDN_STATUS_TIMEOUT = 2     /* an asynchronous copy did not complete within the wait limit */
+};
+
+/*
+ * One fused step in the statequant layout: state [B, HV, K, V], V contiguous.
+ * Replaces ext.gdn_quant_step(14 tensors, qmax, res_fmt, block_v)
+ * (cuda/gdn_state_kernel.cu:310-348, bound at :373-377) and the Triton launch in
+ * statequant/kernel.py:379-408.  Output buffers may alias the matching inputs
+ * (in-place update); they must not partially overlap anything else.
+ */
+typedef struct CarryGdnStepArgs {
+  const int8_t* h_in;      /* [B,HV,K,V] state codes */
+  const float* scale_in;   /* [B,HV,V] (PER_V) or [B,HV] (PER_HEAD) */
+  const void* e_in;        /* residual, [B,HV,K,V] in res_fmt ([.., V/2] bytes for INT4); NULL for RES_NONE */
+  const float* e_scale_in; /* [B,HV,V] or [B,HV]; INT8/INT4 only, else may be NULL */
+  const void* q;           /* [B,HV,K] qkv_dtype */
+  const void* k;           /* [B,HV,K] */
+  const void* v;           /* [B,HV,V] */
+  const float* alpha;      /* [B,HV] decay */
+  const float* beta;       /* [B,HV] write strength */
+  void* o;                 /* [B,HV,V] o_dtype */
+  int8_t* h_out;
+  float* scale_out;
+  void* e_out;
+  float* e_scale_out;
+  int32_t B, HV, K, V;
+  int32_t qkv_dtype;        /* CARRY_F32 | CARRY_BF16 | CARRY_F16 */
+  int32_t o_dtype;
+  float qmax;               /* 2^(bits-1) - 1 */
+  int32_t res_fmt;          /* CARRY_RES_* */
+  int32_t resid_scale_mode; /* CARRY_SCALE_* (INT8/INT4 residual) */
+  int32_t state_scale_mode; /* CARRY_SCALE_* */
+  int32_t eps_mode;         /* CARRY_EPS_* */
+  int32_t* status;          /* optional device word, may be NULL */
+} CarryGdnStepArgs;
+
+int carry_gdn_quant_step(const CarryGdnStepArgs* args, void* stream);
+
+/*
+ * Unquantised fp32 step, state [B, HV, K, V] fp32.  Replaces
+ * ext.gdn_fp32_step (cuda/gdn_state_kernel.cu:350-371) and
+ * statequant/kernel.py:411-433.  h_out may alias h_in.
+ */
+typedef struct CarryGdnFp32Args {
+  const float* h_in;
+  const void* q;
+  const void* k;
+  const void* v;
+  const float* alpha;
+  const float* beta;
+  void* o;
+  float* h_out;
+  int32_t B, HV, K, V;
+  int32_t qkv_dtype;
+  int32_t o_dtype;
+} CarryGdnFp32Args;
+
+int carry_gdn_fp32_step(const CarryGdnFp32Args* args, void* stream);
+
+/*
+ * One slot-indexed step, in place on a paged pool [slots, HV, V, K] (K
+ * contiguous).  Replaces the Triton launch of _quant_int8_kernel
+ * (vllm_integration/quantized_packed_decode.py:303-326; kernel :101-239).
+ * Request n uses slot ssm_state_indices[n]; a slot id <= 0 is padding: zeros go
+ * to out[n] and the pool is not touched.  Two requests must not name the same
+ * slot.  Strides are in elements.
+ */
+typedef struct CarryGdnPackedArgs {
+  const void* mixed_qkv;  /* [B, 2*H*K + HV*V], last stride 1: q | k | v */
+  int64_t stride_mixed_tok;
+  int32_t qkv_dtype;
+  const void* a;          /* [B, HV] */
+  int64_t stride_a_tok;
+  const void* b;          /* [B, HV] */
+  int64_t stride_b_tok;
+  int32_t ab_dtype;
+  const void* A_log;      /* [HV] */
+  int32_t A_log_dtype;
+  const void* dt_bias;    /* [HV] */
+  int32_t dt_bias_dtype;
+  float scale;            /* multiplies q after the optional L2 norm */
+  int8_t* state_codes;    /* [slots, HV, V, K] */
+  float* state_scale;     /* [slots, HV, V] */
+  int8_t* resid_codes;    /* [slots, HV, V, K] (INT8) or [slots, HV, V, K/2] (INT4) */
+  float* resid_scale;     /* [slots, HV, V] (PER_V) or [slots, HV] (PER_HEAD) */
+  int64_t stride_state_slot;
+  int64_t stride_resid_slot;
+  int64_t stride_sscale_slot;
+  int64_t stride_rscale_slot;
+  void* out;              /* [B, 1, HV, V] contiguous */
+  int32_t out_dtype;
+  const int32_t* ssm_state_indices; /* [B] */
+  int64_t stride_indices;
+  int32_t B, H, HV, K, V;
+  int32_t num_slots;
+  int32_t use_qk_l2norm;
+  int32_t res_fmt;          /* CARRY_RES_INT8 | CARRY_RES_INT4 */
+  int32_t resid_scale_mode; /* CARRY_SCALE_* */
+  int32_t eps_mode;         /* CARRY_EPS_* */
+  float qmax;               /* state grid, 127 for 8 bits */
+  int32_t* status;          /* optional device word, may be NULL */
+} CarryGdnPackedArgs;
+
+int carry_gdn_packed_decode(const CarryGdnPackedArgs* args, void* stream);
+
+/* Human-readable text for a CARRY_GDN_ERR_* code (static storage). */
+const char* carry_gdn_strerror(int code);
+
+/* CARRY_GDN_ABI_VERSION the library was built with. */
+int carry_gdn_abi_version(void);
+
+/*
+ * Which kernel the last successful call on this host thread selected:
+ * 0 = none yet, 1 = generic tile kernel, 2 = 128x128 streaming kernel.
+ * Diagnostic only (tests use it to prove which path ran).
+ */
+int carry_gdn_last_kernel(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CARRY_GDN_H_ */

@@ -1,0 +1,173 @@
+"""CPU-only checks of the boundary: the C-ABI library loads and exports what the
+header declares, argument errors come back as codes (no kernel is launched),
+and the Python surfaces keep the reference's names, defaults and exceptions."""
+
+from __future__ import annotations
+
+import ctypes as C
+import inspect
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import gdn_oracle as orc
+
+from carrykernel_b200 import _build, _lib
+from carrykernel_b200.cuda import binding
+from carrykernel_b200.statequant import kernel as sq
+from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(_lib.LIB_PATH):
+        _build.build()
+    return _lib.load_library()
+
+
+def test_header_symbols_are_exported(lib):
+    header = open(os.path.join(ROOT, "include", "carry_gdn.h")).read()
+    declared = set(re.findall(r"\b(carry_gdn_[a-z0-9_]+)\s*\(", header))
+    assert {"carry_gdn_quant_step", "carry_gdn_fp32_step", "carry_gdn_packed_decode",
+            "carry_gdn_strerror", "carry_gdn_abi_version"} <= declared
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in the header but not exported"
+    assert lib.carry_gdn_abi_version() == int(re.search(r"CARRY_GDN_ABI_VERSION (\d+)", header).group(1))
+
+
+def test_struct_sizes_match_header_layout():
+    # pointers 8, int64 8, int32/float 4, natural alignment: field counts from the header
+    assert C.sizeof(_lib.StepArgs) == 14 * 8 + 11 * 4 + 4 + 8
+    assert C.sizeof(_lib.Fp32Args) == 8 * 8 + 6 * 4
+    assert C.sizeof(_lib.PackedArgs) % 8 == 0
+
+
+def test_argument_errors_return_codes_without_a_gpu(lib):
+    assert lib.carry_gdn_quant_step(None, None) == -1
+    assert lib.carry_gdn_fp32_step(None, None) == -1
+    assert lib.carry_gdn_packed_decode(None, None) == -1
+    a = _lib.StepArgs()
+    a.B, a.HV, a.K, a.V, a.qmax = 1, 1, 0, 128, 127.0
+    assert lib.carry_gdn_quant_step(a, None) == -2          # K <= 0
+    a.K = 128
+    a.qkv_dtype = 9
+    assert lib.carry_gdn_quant_step(a, None) == -3          # unknown dtype
+    a.qkv_dtype = 0
+    a.res_fmt = 17
+    assert lib.carry_gdn_quant_step(a, None) == -4          # unknown residual format
+    a.res_fmt = _lib.RES_INT4
+    a.V = 127
+    assert lib.carry_gdn_quant_step(a, None) == -4          # int4 needs an even contiguous length
+    a.V = 128
+    assert lib.carry_gdn_quant_step(a, None) == -1          # pointers missing
+    a.B = 0
+    assert lib.carry_gdn_quant_step(a, None) == 0           # empty batch is a no-op
+    p = _lib.PackedArgs()
+    p.B, p.H, p.HV, p.K, p.V, p.qmax = 1, 3, 4, 32, 16, 127.0
+    assert lib.carry_gdn_packed_decode(p, None) == -2       # HV not a multiple of H
+    p.H = 2
+    p.res_fmt = _lib.RES_FP32
+    assert lib.carry_gdn_packed_decode(p, None) == -4       # slot path is int8/int4 only
+    assert b"NULL" in lib.carry_gdn_strerror(-1)
+    assert lib.carry_gdn_strerror(-99) == b"unknown error code"
+
+
+def test_reference_signatures_are_kept():
+    ps = list(inspect.signature(sq.gdn_quant_step_fused).parameters)
+    assert ps[:12] == ["h_int8", "scale", "e", "e_scale", "q", "k", "v", "alpha", "beta",
+                       "bits", "res_fmt", "BLOCK_V"]
+    d = inspect.signature(sq.gdn_quant_step_fused).parameters
+    assert d["bits"].default == 8 and d["res_fmt"].default == sq.RES_FP32 and d["BLOCK_V"].default == 32
+    assert inspect.signature(binding.gdn_quant_step_cuda).parameters["BLOCK_V"].default == 128
+    assert list(inspect.signature(sq.gdn_step_fused_fp32).parameters) == \
+        ["h", "q", "k", "v", "alpha", "beta", "BLOCK_V"]
+    assert list(inspect.signature(binding.gdn_quant_decode_cuda).parameters)[:10] == \
+        ["h0", "q", "k", "v", "alpha", "beta", "T", "bits", "res_fmt", "BLOCK_V"]
+    assert list(inspect.signature(qpd.quantized_gated_delta_rule_packed_decode).parameters) == [
+        "mixed_qkv", "a", "b", "A_log", "dt_bias", "scale", "state_codes", "state_scale",
+        "resid_codes", "resid_scale", "out", "ssm_state_indices", "use_qk_l2norm_in_kernel",
+        "resid_fmt"]
+    assert (sq.RES_FP32, sq.RES_FP16, sq.RES_FP8, sq.RES_INT8) == (0, 1, 2, 3)
+    assert (qpd.RESID_INT8, qpd.RESID_INT4, qpd.NULL_BLOCK_ID) == (0, 1, 0)
+    assert issubclass(binding.CudaUnavailable, RuntimeError)
+    assert sq.residual_bytes(sq.RES_FP16) == 2 and sq.residual_label(sq.RES_INT8) == "int8"
+    assert sq.residual_dtype(sq.RES_FP8) == torch.float8_e5m2
+
+
+def test_no_cpu_path():
+    h0 = torch.randn(1, 1, 16, 16)
+    st = sq.init_quant_state(h0, 8, sq.RES_INT8)
+    z = torch.zeros(1, 1, 16)
+    with pytest.raises(sq.CudaUnavailable):
+        sq.gdn_quant_step_fused(*st, z, z, z, torch.ones(1, 1), torch.ones(1, 1), res_fmt=sq.RES_INT8)
+    with pytest.raises(AssertionError):
+        sq.gdn_quant_step_fused(st[0].float(), *st[1:], z, z, z, torch.ones(1, 1), torch.ones(1, 1))
+    with pytest.raises(AssertionError):
+        sq.gdn_quant_step_fused(st[0][0], *st[1:], z, z, z, torch.ones(1, 1), torch.ones(1, 1))
+    if not torch.cuda.is_available():
+        with pytest.raises(binding.CudaUnavailable):
+            binding.load_extension()
+
+
+def test_init_matches_oracle():
+    torch.manual_seed(0)
+    h0 = torch.randn(2, 3, 32, 16) * 0.3
+    for fmt in (0, 1, 2, 3, 4):
+        for rs in ("v", "head"):
+            a = sq.init_quant_state(h0, 8, fmt, rs)
+            b = orc.init_quant_state(h0, 8, fmt, rs)
+            for x, y in zip(a, b):
+                assert (x is None and y is None) or (x.dtype == y.dtype and x.shape == y.shape
+                                                     and torch.equal(x.float(), y.float()))
+    pool = torch.randn(4, 3, 16, 32) * 0.1
+    for fmt in (qpd.RESID_INT8, qpd.RESID_INT4):
+        for rs in ("v", "head"):
+            a = qpd.init_quantized_state(4, 3, 16, 32, "cpu", h0=pool, resid_fmt=fmt, resid_scale=rs)
+            b = orc.init_quantized_pool(4, 3, 16, 32, h0=pool, resid_fmt=fmt, resid_scale=rs)
+            for x, y in zip(a, b):
+                assert x.shape == y.shape and torch.equal(x, y)
+
+
+def test_bytes_per_slot():
+    f = qpd.state_bytes_per_slot
+    assert f(32, 128, 128, False, 4) == 2097152
+    assert f(32, 128, 128, False, 2) == 1048576
+    assert f(32, 128, 128, True, resid_fmt=qpd.RESID_INT8) == 1081344
+    assert f(32, 128, 128, True, resid_fmt=qpd.RESID_INT4) == 819200
+    assert f(32, 128, 128, True, resid_fmt=qpd.RESID_INT4, resid_scale="head") == 819200 - 32 * 127 * 4
+
+
+def test_packed_decode_validation_messages():
+    HV, V, K, H, B = 4, 16, 32, 2, 2
+    sc, ss, rc, rs = qpd.init_quantized_state(3, HV, V, K, "cpu")
+    mixed = torch.zeros(B, 2 * H * K + HV * V)
+    a = b = torch.zeros(B, HV)
+    A = d = torch.zeros(HV)
+    out = torch.zeros(B, 1, HV, V)
+    idx = torch.tensor([1, 2], dtype=torch.int32)
+    call = lambda **kw: qpd.quantized_gated_delta_rule_packed_decode(**{**dict(
+        mixed_qkv=mixed, a=a, b=b, A_log=A, dt_bias=d, scale=1.0, state_codes=sc, state_scale=ss,
+        resid_codes=rc, resid_scale=rs, out=out, ssm_state_indices=idx), **kw})
+    with pytest.raises(ValueError, match="2-D"):
+        call(mixed_qkv=mixed[0])
+    with pytest.raises(ValueError, match="4-D"):
+        call(state_codes=sc[0])
+    with pytest.raises(ValueError, match="int8 storage"):
+        call(state_codes=sc.float())
+    with pytest.raises(ValueError, match="packed two codes per byte"):
+        call(resid_fmt=qpd.RESID_INT4)
+    with pytest.raises(ValueError, match="same shape"):
+        call(resid_codes=rc[..., :16])
+    with pytest.raises(ValueError, match="1-D"):
+        call(ssm_state_indices=idx[None])
+    with pytest.raises(ValueError, match="int32"):
+        call(ssm_state_indices=idx.long())
+    with pytest.raises(ValueError, match="out must be"):
+        call(out=out[:, :, :2])
+    with pytest.raises(ValueError, match="cannot infer H"):
+        call(mixed_qkv=torch.zeros(B, HV * V + 3))
+    with pytest.raises(qpd.CudaUnavailable):
+        call()
