@@ -1,0 +1,477 @@
+"""Benchmark of the fused GDN decode step on a quantized state (B200).
+
+Workload (one "step" = one decode step of the whole job on one GPU): 64
+requests advance one token through 24 stacked GDN layers.  Each layer has its
+own paged pool of 256 slots (+ padding slot 0) addressed through a random
+permutation of slot ids; H = HV = 32 heads, K = V = 128; int8 state with
+per-V-row scales, packed int4 error-feedback residual with one scale per head;
+q | k | v, a, b and the output in bf16; q, k L2-normalised in the kernel; decay
+exp(-0.1 softplus(N(0,1))), write strength sigmoid(N(0,1)); the initial state is
+64 warm-up steps of the same process.  All inputs are synthetic and seeded.
+
+With N GPUs every rank runs that same per-GPU workload on its own slots (the
+pool is sharded by slot: 64 N requests in total, weak scaling) and there is no
+collective on the data path; NCCL only carries the barrier and the max over
+ranks of the elapsed time.
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference --steps 20 --warmup 5     # CPU arm (oracle port)
+
+One JSON line goes to stdout (rank 0).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+H = HV = 32
+K = V = 128
+LAYERS = 24
+BATCH = 64
+POOL_SLOTS = 256
+WARM_STEPS = 64
+METRIC = "gdn_state_step_throughput"
+UNIT = "slot-layer-steps/s"
+
+# algorithmic bytes of one (slot, head) tile, each byte counted once per step:
+# int8 state r+w, packed int4 residual r+w, fp32 per-V state scale r+w, per-head
+# residual scale r+w, bf16 q, k, v, fp32-equivalent gate inputs (a, b as 2 x 4 B),
+# bf16 output row
+TILE_BYTES = 2 * K * V + 2 * (K * V // 2) + 2 * V * 4 + 2 * 4 + 2 * K * 2 + V * 2 + 2 * 4 + V * 2
+SLOT_LAYER_BYTES = HV * TILE_BYTES + 4          # + the int32 slot id
+assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
+# kernel on this workload (64 requests), from the ncu capture summarised under
+# profiles/; None until a capture exists.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def parse_args():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU per step")
+    ap.add_argument("--layers", type=int, default=LAYERS)
+    ap.add_argument("--resid", choices=["int4", "int8"], default="int4")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    return ap.parse_args()
+
+
+def peak_hbm():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------
+# workload
+# ---------------------------------------------------------------------------
+
+class Workload:
+    """Per-GPU state and inputs of the decode step, resident in HBM."""
+
+    def __init__(self, device, batch, layers, resid, seed):
+        from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+        self.qpd, self.device, self.batch, self.layers = qpd, device, batch, layers
+        self.resid_fmt = qpd.RESID_INT4 if resid == "int4" else qpd.RESID_INT8
+        g = torch.Generator().manual_seed(seed)
+        width = 2 * H * K + HV * V
+        slots = max(POOL_SLOTS, batch) + 1
+        self.num_slots = slots
+        self.pools, self.indices, self.mixed, self.a, self.b, self.out = [], [], [], [], [], []
+        for _ in range(layers):
+            self.pools.append(qpd.init_quantized_state(slots, HV, V, K, device,
+                                                       resid_fmt=self.resid_fmt, resid_scale="head"))
+            self.indices.append((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32).to(device))
+            self.mixed.append(torch.randn(batch, width, generator=g).to(torch.bfloat16).to(device))
+            self.a.append(torch.randn(batch, HV, generator=g).to(torch.bfloat16).to(device))
+            self.b.append(torch.randn(batch, HV, generator=g).to(torch.bfloat16).to(device))
+            self.out.append(torch.empty(batch, 1, HV, V, dtype=torch.bfloat16, device=device))
+        self.A_log = torch.full((HV,), math.log(0.1), device=device)
+        self.dt_bias = torch.zeros(HV, device=device)
+        self.scale = K ** -0.5
+        # alternative activations, so the warm-up process is not one repeated token
+        self.warm_mixed = [torch.randn(batch, width, generator=g).to(torch.bfloat16).to(device) for _ in range(4)]
+
+    def layer_step(self, l, mixed=None, a=None, b=None, idx=None, out=None):
+        self.qpd.quantized_gated_delta_rule_packed_decode(
+            self.mixed[l] if mixed is None else mixed, self.a[l] if a is None else a,
+            self.b[l] if b is None else b, self.A_log, self.dt_bias, self.scale,
+            *self.pools[l], self.out[l] if out is None else out,
+            self.indices[l] if idx is None else idx,
+            use_qk_l2norm_in_kernel=True, resid_fmt=self.resid_fmt)
+
+    def step(self):
+        for l in range(self.layers):
+            self.layer_step(l)
+
+    def warm_state(self, steps=WARM_STEPS):
+        for t in range(steps):
+            for l in range(self.layers):
+                self.layer_step(l, mixed=self.warm_mixed[(t + l) % 4])
+        torch.cuda.synchronize(self.device)
+
+
+# ---------------------------------------------------------------------------
+# measurement helpers
+# ---------------------------------------------------------------------------
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples of one GPU during a region."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc, self.path = gpu_index, None, None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile("w", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def physical_gpu_index(local_rank):
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        ids = [x for x in vis.split(",") if x.strip()]
+        if local_rank < len(ids) and ids[local_rank].strip().isdigit():
+            return int(ids[local_rank])
+    return local_rank
+
+
+def time_graph(graph, steps, device):
+    """Device time of ``steps`` replays, CUDA events on the launching stream."""
+    stream = torch.cuda.current_stream(device)
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(device)
+    start.record(stream)
+    for _ in range(steps):
+        graph.replay()
+    end.record(stream)
+    torch.cuda.synchronize(device)
+    return start.elapsed_time(end) * 1e-3
+
+
+def e2e_run(wl, steps, warmup):
+    """The same step through the public call with HOST buffers: every layer's
+    activations and slot ids are copied from pinned host memory, the layer is
+    launched, and its output row block is copied back to pinned host memory;
+    the step ends with a stream synchronise (the host holds every output)."""
+    dev = wl.device
+    L = wl.layers
+    host_in = [[t.cpu().pin_memory() for t in (wl.mixed[l], wl.a[l], wl.b[l], wl.indices[l])] for l in range(L)]
+    host_out = [torch.empty(wl.out[l].shape, dtype=wl.out[l].dtype).pin_memory() for l in range(L)]
+    dev_in = [[torch.empty_like(t, device=dev) for t in host_in[l]] for l in range(L)]
+    h2d = sum(t.numel() * t.element_size() for t in host_in[0]) * L
+    d2h = host_out[0].numel() * host_out[0].element_size() * L
+
+    def one_step():
+        for l in range(L):
+            for d, h in zip(dev_in[l], host_in[l]):
+                d.copy_(h, non_blocking=True)
+            wl.layer_step(l, *dev_in[l][:3], idx=dev_in[l][3])
+            host_out[l].copy_(wl.out[l], non_blocking=True)
+        torch.cuda.synchronize(dev)
+
+    for _ in range(warmup):
+        one_step()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    start.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize(dev)
+    wall = time.perf_counter() - t0
+    return max(wall, start.elapsed_time(end) * 1e-3), h2d, d2h
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle port, timed on the host cores; doubles as the checker
+# ---------------------------------------------------------------------------
+
+def cpu_sample_inputs(batch, layers, resid, seed=1234):
+    """CPU copy of a bounded sample of the workload (same shapes and laws)."""
+    from oracle import gdn_oracle as orc
+    g = torch.Generator().manual_seed(seed)
+    fmt = orc.RESID_INT4 if resid == "int4" else orc.RESID_INT8
+    width = 2 * H * K + HV * V
+    sample = []
+    for _ in range(layers):
+        pool = torch.randn(batch + 1, HV, V, K, generator=g) * 0.124
+        st = list(orc.init_quantized_pool(batch + 1, HV, V, K, h0=pool, resid_fmt=fmt, resid_scale="head"))
+        idx = (torch.randperm(batch, generator=g) + 1).to(torch.int32)
+        mixed = torch.randn(batch, width, generator=g).to(torch.bfloat16)
+        a = torch.randn(batch, HV, generator=g).to(torch.bfloat16)
+        b = torch.randn(batch, HV, generator=g).to(torch.bfloat16)
+        sample.append((st, idx, mixed, a, b))
+    return sample, fmt
+
+
+def cpu_oracle_pass(sample, fmt):
+    from oracle import gdn_oracle as orc
+    A_log = torch.full((HV,), math.log(0.1))
+    dt_bias = torch.zeros(HV)
+    outs = []
+    for st, idx, mixed, a, b in sample:
+        out = torch.empty(mixed.shape[0], 1, HV, V, dtype=torch.bfloat16)
+        orc.packed_decode_step(mixed, a, b, A_log, dt_bias, K ** -0.5, *st, out, idx,
+                               use_qk_l2norm_in_kernel=True, resid_fmt=fmt)
+        outs.append(out)
+    return outs
+
+
+def time_cpu_oracle(batch, layers, resid, passes, warm=1):
+    """Seconds per pass of the oracle over the sample (all host threads)."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample, fmt = cpu_sample_inputs(batch, layers, resid)
+    for _ in range(warm):
+        cpu_oracle_pass(sample, fmt)
+    times = []
+    for _ in range(passes):
+        t0 = time.perf_counter()
+        cpu_oracle_pass(sample, fmt)
+        times.append(time.perf_counter() - t0)
+    return sum(times) / len(times), batch * layers
+
+
+def cpu_baseline_and_parity(wl, resid):
+    """Time the oracle on a bounded sample and, on that same sample, check the
+    GPU step against it (validate before timing)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle import gdn_oracle as orc
+    import parity
+    s_batch, s_layers = min(wl.batch, 16), 2
+    sample, fmt = cpu_sample_inputs(s_batch, s_layers, resid)
+    # GPU result on the sample (teacher-forced from the same start state)
+    dev = wl.device
+    f_state = f_resid = 0.0
+    gpu_outs, gpu_pools = [], []
+    for st, idx, mixed, a, b in sample:
+        pool = [x.clone().to(dev) for x in st]
+        out = torch.empty(s_batch, 1, HV, V, dtype=torch.bfloat16, device=dev)
+        wl.qpd.quantized_gated_delta_rule_packed_decode(
+            mixed.to(dev), a.to(dev), b.to(dev), wl.A_log, wl.dt_bias, wl.scale, *pool, out, idx.to(dev),
+            use_qk_l2norm_in_kernel=True, resid_fmt=wl.resid_fmt)
+        gpu_outs.append(out.cpu()); gpu_pools.append([x.cpu() for x in pool])
+    torch.set_num_threads(os.cpu_count() or 1)
+    t0 = time.perf_counter()
+    cpu_outs = cpu_oracle_pass(sample, fmt)
+    first = time.perf_counter() - t0
+    for (st, idx, *_), go, gp, co in zip(sample, gpu_outs, gpu_pools, cpu_outs):
+        parity.assert_close(go, co, "bench: out", rtol=8e-3, atol=1e-4)
+        fs, fr = parity.check_pool(gp, st, fmt == orc.RESID_INT4, idx.tolist(), orc.unpack_int4, "bench")
+        f_state, f_resid = max(f_state, fs), max(f_resid, fr)
+    # timing: enough passes for roughly 10-20 s of CPU work
+    passes = max(2, min(20, int(12.0 / max(first, 1e-3))))
+    sec, units = time_cpu_oracle(s_batch, s_layers, resid, passes, warm=0)
+    return ({"value": units / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+             "sample": f"{s_layers} layers x {s_batch} requests of the same workload "
+                       f"({units} slot-layer-steps per pass, {passes} passes, torch CPU oracle)"},
+            {"state_flip_frac": f_state, "resid_flip_frac": f_resid, "checked_slot_layer_steps": units,
+             "limit": parity.MAX_FLIP_FRAC})
+
+
+def run_reference_arm(args, rank):
+    """--impl reference: the reference's CPU algorithm (oracle port) on the host
+    cores.  One step is a bounded sample: 1 layer x 16 requests."""
+    if rank != 0:
+        return
+    s_batch, s_layers = 16, 1
+    torch.set_num_threads(os.cpu_count() or 1)
+    sample, fmt = cpu_sample_inputs(s_batch, s_layers, args.resid)
+    for _ in range(max(args.warmup, 1)):
+        cpu_oracle_pass(sample, fmt)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_oracle_pass(sample, fmt)
+    sec = time.perf_counter() - t0
+    units = s_batch * s_layers * args.steps
+    value = units / sec
+    desc = f"{s_layers} layer x {s_batch} requests per step (same shapes and input laws)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": workload_config(args, args.batch, args.layers),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args, batch, layers, note=None):
+    cfg = {"workload": "slot-indexed GDN decode step: int8 state + packed int4 residual (per-head "
+                       "residual scale), 24 layers x 64 requests per GPU, pools of 256 slots"
+                       if (args.resid == "int4" and batch == BATCH and layers == LAYERS) else
+                       f"slot-indexed GDN decode step, {args.resid} residual",
+           "requests_per_gpu": batch, "layers": layers, "H": H, "HV": HV, "K": K, "V": V,
+           "pool_slots": POOL_SLOTS, "resid": args.resid, "resid_scale": "per-head",
+           "activations": "bf16", "parallelism": f"slot-sharded x{args.gpus}, no collective",
+           "l2": "inputs larger than L2: each step touches a different 52 MB of state per layer, "
+                 "1.26 GB per step against 126 MB of L2"}
+    if note:
+        cfg["sample"] = note
+    return cfg
+
+
+# ---------------------------------------------------------------------------
+# main
+# ---------------------------------------------------------------------------
+
+def main():
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference_arm(args, rank)
+        return
+
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    n_gpus = world
+
+    from carrykernel_b200 import _lib
+    lib = _lib.load_library()
+
+    wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank)
+    wl.warm_state()
+    kernel_used = lib.carry_gdn_last_kernel()
+
+    cpu_base = parity_stats = None
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+        cpu_base, parity_stats = cpu_baseline_and_parity(wl, args.resid)
+
+    # capture one decode step (all layers) in a CUDA graph
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        wl.step()
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        wl.step()
+    for _ in range(max(args.warmup, 3)):
+        graph.replay()
+    torch.cuda.synchronize(device)
+
+    sampler = ClockSampler(physical_gpu_index(local_rank))
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    sampler.start()
+    elapsed = time_graph(graph, args.steps, device)
+    # keep the sampler alive long enough for at least a few samples under load
+    if elapsed < 0.5:
+        reps = int(0.5 / max(elapsed / args.steps, 1e-6)) + 1
+        time_graph(graph, reps, device)
+    clocks = sampler.stop()
+    if world > 1:
+        dist.barrier()
+    from carrykernel_b200.sharding import max_over_ranks
+    elapsed = max_over_ranks(elapsed, device)
+
+    units_per_step = args.batch * args.layers * n_gpus
+    value = units_per_step * args.steps / elapsed
+    per_launch = elapsed / (args.steps * args.layers)
+    peak, peak_kind = peak_hbm()
+    achieved = SLOT_LAYER_BYTES * args.batch / per_launch / 1e9 if args.resid == "int4" else \
+        (SLOT_LAYER_BYTES + HV * K * V) * args.batch / per_launch / 1e9
+
+    e2e = None
+    if not args.no_e2e:
+        t_e2e, h2d, d2h = e2e_run(wl, args.steps, max(args.warmup, 3))
+        t_e2e = max_over_ranks(t_e2e, device)
+        e2e = {"value": units_per_step * args.steps / t_e2e, "unit": UNIT,
+               "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+               "ms_per_step": t_e2e / args.steps * 1e3}
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": elapsed / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": workload_config(args, args.batch, args.layers),
+            "us_per_token": elapsed / args.steps * 1e6,
+            "us_per_layer_step": per_launch * 1e6,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                         "frac_of_8000": achieved / 8000.0,
+                         "bytes_per_launch": SLOT_LAYER_BYTES * args.batch,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "kernel": {1: "gdn_generic_kernel", 2: "gdn_tile128_kernel"}.get(kernel_used, "?")},
+            "cpu_baseline": cpu_base, "parity": parity_stats, "e2e": e2e,
+            "gpu_launches": args.steps * args.layers, "clocks": clocks,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
