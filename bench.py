@@ -71,6 +71,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU per step")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--resid", choices=["int4", "int8"], default="int4")
+    ap.add_argument("--warm-steps", type=int, default=WARM_STEPS,
+                    help="untimed steps that build the initial state (64 = the named workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -400,7 +402,7 @@ def main():
     lib = _lib.load_library()
 
     wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank)
-    wl.warm_state()
+    wl.warm_state(args.warm_steps)
     kernel_used = lib.carry_gdn_last_kernel()
 
     cpu_base = parity_stats = None

@@ -1,0 +1,902 @@
+// Streaming kernel for the serving shape: K = V = 128, int8 state, int8 or packed
+// int4 residual.  One (request, head) tile is 16 KB of codes + 8/16 KB of
+// residual; all of it is contiguous in memory in both layouts, so every tile
+// moves with a handful of 1-D bulk async copies (TMA, no tensor map):
+//
+//   global --cp.async.bulk--> shared stage --(registers)--> same shared stage
+//          --cp.async.bulk--> global
+//
+// Persistent CTAs (two per SM) walk the tile list with a ring of stages: while
+// one tile is computed, the loads of the next ones are in flight and the stores
+// of the previous one drain.  The state is read from HBM once and written once.
+//
+// Work split inside a CTA (256 threads = 8 warps): warp w owns memory rows
+// 16w..16w+15 of the tile.
+//   * slot layout [V][K] (scale per row): lane = (row group rg, column group
+//     cg): 4 rows x 16 contiguous columns.  Everything the math reduces over
+//     (K) lies along the row, so reductions are 3 shuffle steps inside 8 lanes
+//     and warps never wait for each other, except once per tile when the
+//     residual scale is per head.
+//   * statequant layout [K][V] (scale per column): lane = 4 contiguous columns
+//     x the warp's 16 rows; column sums are finished across the 8 warps through
+//     shared memory.
+// Each warp stores its own 16 rows back, so no CTA-wide barrier guards stores.
+//
+// Arithmetic keeps the reference's operation order for everything that feeds a
+// state code: (code*scale)*alpha, h + (k*dv) with the product rounded first,
+// target - (code*scale) with the product rounded first.  round(target / s) is
+// evaluated as rint(target * (1/s)); the two can only differ when the quotient
+// is within ~3e-5 of a tie, which shows up as a remainder within 2^-14 of half
+// a step -- groups of elements where that happens are re-decided with the true
+// division.  Residual codes use rint(e * (1/es)) as is.  Math runs as packed
+// f32x2 (IEEE round-to-nearest per component).
+#pragma once
+#include "carry_gdn_common.cuh"
+
+namespace carry {
+namespace {
+
+constexpr int kT = 128;                 // tile edge
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kTileCache = 128;         // per-CTA cache of slot ids and gates for its first tiles
+
+enum { LAYOUT_VK = 0, LAYOUT_KV = 1 };  // slot layout [V][K]; statequant layout [K][V]
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst_smem)),
+               "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem),
+               "r"(smem_u32(src_smem)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Bounded wait: after kSpinLimit failed polls the CTA is marked poisoned, the
+// status word gets the timeout bit and every later wait returns at once; a
+// poisoned CTA stops loading and storing.
+__device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* poison, int* status) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (mbar_try_wait(bar, parity)) return;
+    if (spin > 64) __nanosleep(64);
+    if ((spin & 1023) == 1023 && *poison) return;
+  }
+  *poison = 1;
+  if (status) atomicOr(status, CARRY_GDN_STATUS_TIMEOUT);
+}
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* poison, int* status) {
+  if (*poison) return;
+  if (mbar_try_wait(bar, parity)) return;
+  mbar_wait_slow(bar, parity, poison, status);
+}
+
+// All 8 warps meet here: one arrival per warp, then a bounded wait (never a
+// bar.sync inside the tile loop, so nothing in it can wait without a limit).
+__device__ __forceinline__ void warps_meet(uint64_t* bar, uint32_t parity, int lane, volatile int* poison,
+                                           int* status) {
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar);
+  mbar_wait(bar, parity, poison, status);
+}
+
+// ---------------------------------------------------------------------------
+// packed fp32 helpers (each maps to one f32x2 instruction)
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 add2(float2 a, float2 b) { return __fadd2_rn(a, b); }
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 splat(float x) { return make_float2(x, x); }
+__device__ __forceinline__ float max3abs(float m, float2 x) { return fmaxf(fmaxf(m, fabsf(x.x)), fabsf(x.y)); }
+
+constexpr float kMagicRound = 12582912.0f;      // 1.5 * 2^23: x + M rounds x to an integer (RNE)
+constexpr float kMagicByte = 8388736.0f;        // 2^23 + 128
+constexpr float kMagicNib = 8388616.0f;         // 2^23 + 8
+constexpr float kTieGuard = 0.49993896484375f;  // 0.5 - 2^-14
+
+// bytes A and B of w (each already XOR-ed with 0x80) -> {float(code A), float(code B)}
+template <int A, int B>
+__device__ __forceinline__ float2 s8x2_to_float(uint32_t w) {
+  const float2 m = make_float2(__uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 | A)),
+                               __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 | B)));
+  return add2(m, splat(-kMagicByte));
+}
+// bytes A and B of w (each nibble already XOR-ed with 8): {low nibbles}, {16 * high nibbles}
+template <int A, int B>
+__device__ __forceinline__ void s4x4_to_float(uint32_t w, float2& lo, float2& hi16) {
+  const uint32_t a = __byte_perm(w, 0x4B000000u, 0x7440 | A), b = __byte_perm(w, 0x4B000000u, 0x7440 | B);
+  lo = add2(make_float2(__uint_as_float(a & 0xFFFFFF0Fu), __uint_as_float(b & 0xFFFFFF0Fu)), splat(-kMagicNib));
+  hi16 = add2(make_float2(__uint_as_float(a & 0xFFFFFFF0u), __uint_as_float(b & 0xFFFFFFF0u)), splat(-kMagicByte));
+}
+// low bytes of four words -> one word (a | b<<8 | c<<16 | d<<24)
+__device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
+}
+
+__device__ __forceinline__ float warp_sum8(float x) {   // over the 8 lanes sharing a row group
+  x += __shfl_xor_sync(0xffffffffu, x, 1);
+  x += __shfl_xor_sync(0xffffffffu, x, 2);
+  x += __shfl_xor_sync(0xffffffffu, x, 4);
+  return x;
+}
+__device__ __forceinline__ float warp_max8(float x) {
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
+  return x;
+}
+__device__ __forceinline__ float warp_sum32(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+__device__ __forceinline__ float warp_max32(float x) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+  return x;
+}
+
+// ---------------------------------------------------------------------------
+// shared-memory stage layout (bytes)
+// ---------------------------------------------------------------------------
+template <int RES, int LAYOUT = 0>
+struct StageLayout {
+  static constexpr int kResidBytes = (RES == CARRY_RES_INT4) ? kT * kT / 2 : kT * kT;
+  static constexpr int kCodes = 0;
+  static constexpr int kResid = kT * kT;
+  static constexpr int kSScale = kResid + kResidBytes;       // 128 floats
+  static constexpr int kRScale = kSScale + 512;              // 128 floats (per V) or a row of per-head scales
+  static constexpr int kQ = kRScale + 512;                   // raw q, up to 128 x 4 B
+  static constexpr int kK = kQ + 512;
+  static constexpr int kV = kK + 512;
+  static constexpr int kHeader = kV + 512;                   // int slot
+  static constexpr int kBytes = kHeader + 16;
+  // slot layout: two CTAs per SM; the statequant layout also needs 16 KB of
+  // cross-warp reduction space, so its int8-residual variant runs one CTA per SM
+  static constexpr int kCtasPerSm = (LAYOUT == 1 && RES != CARRY_RES_INT4) ? 1 : 2;
+  static constexpr int kStages = (LAYOUT == 0) ? ((RES == CARRY_RES_INT4) ? 4 : 3)
+                                               : ((RES == CARRY_RES_INT4) ? 3 : 5);
+};
+
+__device__ __forceinline__ int esize(int dtype) { return dtype == CARRY_F32 ? 4 : 2; }
+
+__device__ __forceinline__ float raw_to_float(const uint8_t* base, int i, int dtype) {
+  if (dtype == CARRY_F32) return reinterpret_cast<const float*>(base)[i];
+  if (dtype == CARRY_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
+  return __half2float(reinterpret_cast<const __half*>(base)[i]);
+}
+
+
+// activations of one head as they sit in the stage (element type QDT) -> fp32
+template <int QDT>
+__device__ __forceinline__ float act(const uint8_t* base, int i) {
+  if (QDT == CARRY_F32) return reinterpret_cast<const float*>(base)[i];
+  if (QDT == CARRY_BF16) return __uint_as_float((uint32_t)reinterpret_cast<const uint16_t*>(base)[i] << 16);
+  return __half2float(reinterpret_cast<const __half*>(base)[i]);
+}
+// two consecutive 16-bit activations packed in one word -> {first, second}
+template <int QDT>
+__device__ __forceinline__ float2 act_pair(uint32_t w) {
+  if (QDT == CARRY_BF16) return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+  return __half22float2(*reinterpret_cast<const __half2*>(&w));
+}
+// four consecutive activations starting at element `first` (a multiple of 4)
+template <int QDT>
+__device__ __forceinline__ float4 act4(const uint8_t* base, int first) {
+  if (QDT == CARRY_F32) return *reinterpret_cast<const float4*>(base + first * 4);
+  const uint2 w = *reinterpret_cast<const uint2*>(base + first * 2);
+  const float2 a = act_pair<QDT>(w.x), b = act_pair<QDT>(w.y);
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+// 16 consecutive activations starting at `first` (a multiple of 16), as column pairs per quad:
+// E[m] = {x[4m], x[4m+2]}, O[m] = {x[4m+1], x[4m+3]}, each times `mul`
+template <int QDT>
+__device__ __forceinline__ void act16_pairs(const uint8_t* base, int first, float mul, float2 (&E)[4], float2 (&O)[4]) {
+  const float2 m2 = make_float2(mul, mul);
+  if (QDT == CARRY_F32) {
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const float4 x = *reinterpret_cast<const float4*>(base + (first + 4 * m) * 4);
+      E[m] = __fmul2_rn(make_float2(x.x, x.z), m2);
+      O[m] = __fmul2_rn(make_float2(x.y, x.w), m2);
+    }
+  } else {
+    const uint4 lo = *reinterpret_cast<const uint4*>(base + first * 2);
+    const uint4 hi = *reinterpret_cast<const uint4*>(base + first * 2 + 16);
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int m = 0; m < 4; ++m) {
+      const float2 a = act_pair<QDT>(w[2 * m]), b = act_pair<QDT>(w[2 * m + 1]);
+      E[m] = __fmul2_rn(make_float2(a.x, b.x), m2);
+      O[m] = __fmul2_rn(make_float2(a.y, b.y), m2);
+    }
+  }
+}
+
+__device__ __noinline__ float exact_code(float t, float s) { return rintf(__fdiv_rn(t, s)); }
+
+// Re-decide one element whose remainder sits within the tie guard: the code is
+// rint of the true quotient.  `y` is code + kMagicRound, `e` the remainder.
+__device__ __forceinline__ void redecide(float& e, float& y, float s, float thr) {
+  if (fabsf(e) > thr) {
+    const float code_old = __fadd_rn(y, -kMagicRound);
+    const float t = __fadd_rn(e, __fmul_rn(code_old, s));     // exact: the remainder was formed exactly
+    const float code = exact_code(t, s);
+    y = __fadd_rn(code, kMagicRound);
+    e = __fadd_rn(t, -__fmul_rn(code, s));
+  }
+}
+
+// gates of one (request, head): derived in the kernel on the slot path, given on the other
+__device__ __noinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta) {
+  if (p.packed) {
+    slot_gates(load_as_float(p.a, (long long)n * p.stride_a_tok + hv, p.ab_dtype),
+               load_as_float(p.b, (long long)n * p.stride_b_tok + hv, p.ab_dtype),
+               load_as_float(p.A_log, hv, p.A_log_dtype), load_as_float(p.dt_bias, hv, p.dt_bias_dtype),
+               alpha, beta);
+  } else {
+    alpha = p.alpha[(long long)n * p.HV + hv];
+    beta = p.beta[(long long)n * p.HV + hv];
+  }
+}
+
+// Load tile `it` of this CTA into stage it % S (called by one thread).
+template <int LAYOUT, int RES, int RSCALE>
+__device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_t* full_bar, const int* slot_cache,
+                                        int it) {
+  using L = StageLayout<RES, LAYOUT>;
+  constexpr int S = L::kStages;
+  const int qes = esize(p.qkv_dtype);
+  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
+  const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+  const int n = tile / p.HV, hv = tile - n * p.HV;
+  uint8_t* sb = smem + (size_t)(it % S) * L::kBytes;
+  long long slot = 1;
+  if (p.packed) {
+    slot = (it < kTileCache) ? slot_cache[it] : p.slot_idx[(long long)n * p.stride_idx];
+    if (slot >= p.num_slots) {
+      if (p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
+      slot = 0;
+    }
+  }
+  *reinterpret_cast<volatile int*>(sb + L::kHeader) = (int)slot;
+  uint64_t* bar = &full_bar[it % S];
+  if (slot <= 0) { mbar_arrive(bar); return; }
+  constexpr long long KV = kT * kT;
+  const int8_t* codes;
+  const uint8_t *resid, *q, *k, *v;
+  const float *sscale, *rscale;
+  if (p.packed) {
+    codes = p.codes_in + slot * p.stride_state_slot + hv * KV;
+    resid = reinterpret_cast<const uint8_t*>(p.resid_in) + slot * p.stride_resid_slot + (long long)hv * L::kResidBytes;
+    sscale = p.sscale_in + slot * p.stride_sscale_slot + (long long)hv * kT;
+    rscale = p.rscale_in + slot * p.stride_rscale_slot + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : 0);
+    const int h = hv / (p.HV / p.H);
+    const uint8_t* row = reinterpret_cast<const uint8_t*>(p.q) + (long long)n * p.stride_mixed_tok * qes;
+    q = row + (long long)h * kT * qes;
+    k = row + ((long long)p.H * kT + (long long)h * kT) * qes;
+    v = row + (2LL * p.H * kT + (long long)hv * kT) * qes;
+  } else {
+    const long long nh = (long long)n * p.HV + hv;
+    codes = p.codes_in + nh * KV;
+    resid = reinterpret_cast<const uint8_t*>(p.resid_in) + nh * L::kResidBytes;
+    sscale = p.sscale_in + nh * kT;
+    rscale = p.rscale_in + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : (long long)n * p.HV);
+    q = reinterpret_cast<const uint8_t*>(p.q) + nh * kT * qes;
+    k = reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes;
+    v = reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes;
+  }
+  const uint32_t vec = (uint32_t)kT * qes;
+  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * vec);
+  bulk_load(sb + L::kCodes, codes, kT * kT, bar);
+  bulk_load(sb + L::kResid, resid, L::kResidBytes, bar);
+  bulk_load(sb + L::kSScale, sscale, 512, bar);
+  bulk_load(sb + L::kRScale, rscale, rscale_bytes, bar);
+  bulk_load(sb + L::kQ, q, vec, bar);
+  bulk_load(sb + L::kK, k, vec, bar);
+  bulk_load(sb + L::kV, v, vec, bar);
+}
+
+// ---------------------------------------------------------------------------
+// the kernel
+// ---------------------------------------------------------------------------
+template <int LAYOUT, int RES, int RSCALE, int QDT>
+__global__ void __launch_bounds__(kThreads, (StageLayout<RES, LAYOUT>::kCtasPerSm))
+gdn_tile128_kernel(const __grid_constant__ KParams p) {
+  using L = StageLayout<RES, LAYOUT>;
+  constexpr int S = L::kStages;
+  extern __shared__ __align__(128) uint8_t smem[];
+  __shared__ __align__(8) uint64_t full_bar[S];
+  __shared__ __align__(8) uint64_t meet_bar[3];
+  __shared__ int done_cnt[S];                        // warps whose stores of a stage have left shared memory
+  __shared__ int poison_flag;
+  __shared__ float head_red[2][kWarps];
+  __shared__ int slot_cache[kTileCache];             // slot ids of this CTA's first tiles
+  __shared__ float alpha_cache[kTileCache], beta_cache[kTileCache];
+  __shared__ __align__(16) float col_red[(LAYOUT == LAYOUT_KV) ? kWarps * kT * 4 : 4];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int total = p.B * p.HV;
+  const int my_tiles = (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  volatile int* poison = &poison_flag;
+
+  if (tid == 0) {
+    poison_flag = 0;
+    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
+    for (int s = 0; s < 3; ++s) mbar_init(&meet_bar[s], kWarps);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // slot ids and gates of this CTA's first tiles: one trip to global memory, up front
+  for (int i = tid; i < my_tiles && i < kTileCache; i += kThreads) {
+    const int tile = (int)blockIdx.x + i * (int)gridDim.x;
+    const int n = tile / p.HV, hv = tile - n * p.HV;
+    slot_cache[i] = p.packed ? p.slot_idx[(long long)n * p.stride_idx] : 1;
+    float a, b;
+    gates_of(p, n, hv, a, b);
+    alpha_cache[i] = a;
+    beta_cache[i] = b;
+  }
+  __syncthreads();
+
+  if (tid == 0) {
+    const int pre = my_tiles < S ? my_tiles : S;
+    for (int it = 0; it < pre; ++it) issue_tile<LAYOUT, RES, RSCALE>(p, smem, full_bar, slot_cache, it);
+  }
+
+  const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
+  uint32_t meet_parity = 0;            // flips once per computed tile
+
+  for (int it = 0; it < my_tiles; ++it) {
+    const int s = it % S;
+    const uint32_t parity = (uint32_t)(it / S) & 1u;
+    uint8_t* sb = smem + (size_t)s * L::kBytes;
+    const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+    const int n = tile / p.HV, hv = tile - n * p.HV;
+
+    mbar_wait(&full_bar[s], parity, poison, p.status);
+    const int slot = *reinterpret_cast<volatile int*>(sb + L::kHeader);
+    const long long out_off = ((long long)n * p.HV + hv) * kT;
+    const bool live = slot > 0 && !*poison;
+
+    if (!live) {
+      if (slot <= 0 && tid < kT) store_from_float(p.out, out_off + tid, p.o_dtype, 0.f);
+    } else {
+      float alpha, beta;
+      if (it < kTileCache) { alpha = alpha_cache[it]; beta = beta_cache[it]; }
+      else gates_of(p, n, hv, alpha, beta);
+
+      float k_mul = 1.0f, q_mul = 1.0f;
+      if (p.packed) {
+        if (p.l2norm) {                 // every warp on its own: 4 elements per lane, then a warp sum
+          const float4 k4 = act4<QDT>(sb + L::kK, 4 * lane), q4 = act4<QDT>(sb + L::kQ, 4 * lane);
+          const float ks = fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w)));
+          const float qs = fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w)));
+          k_mul = __frcp_rn(sqrtf(warp_sum32(ks) + 1e-6f));
+          q_mul = __frcp_rn(sqrtf(warp_sum32(qs) + 1e-6f));
+        }
+        q_mul *= p.qscale;
+      }
+      const float* sscale = reinterpret_cast<const float*>(sb + L::kSScale);
+      const float* rscale = reinterpret_cast<const float*>(sb + L::kRScale);
+      const float es_head = (RSCALE == CARRY_SCALE_PER_HEAD) ? rscale[hv] : 0.f;
+      const float2 alpha2 = splat(alpha);
+      const float2 magic2 = splat(kMagicRound), nmagic2 = splat(-kMagicRound);
+
+      if constexpr (LAYOUT == LAYOUT_VK) {
+        // lane: rows r0..r0+3, columns c0..c0+15.  A quad of columns (one 32-bit
+        // word of codes) is held as two pairs: E = {col 0, col 2}, O = {col 1, col 3}.
+        const int cg = lane & 7, rg = lane >> 3;
+        const int r0 = 16 * warp + 4 * rg, c0 = 16 * cg;
+        float2 kE[4], kO[4], qE[4], qO[4];
+        act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
+        act16_pairs<QDT>(sb + L::kQ, c0, q_mul, qE, qO);
+        float kq;
+        {
+          float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int m = 0; m < 4; ++m) { acc = fma2(kE[m], qE[m], acc); acc = fma2(kO[m], qO[m], acc); }
+          kq = warp_sum8(acc.x + acc.y);
+        }
+
+        float2 hE[4][4], hO[4][4];       // [row][quad]
+        float dk[4], dq[4], srow[4], vrow[4];
+        {
+          const float4 s4 = *reinterpret_cast<const float4*>(sscale + r0);
+          srow[0] = s4.x; srow[1] = s4.y; srow[2] = s4.z; srow[3] = s4.w;
+          const float4 v4 = act4<QDT>(sb + L::kV, r0);
+          vrow[0] = v4.x; vrow[1] = v4.y; vrow[2] = v4.z; vrow[3] = v4.w;
+        }
+        // phase 1: dequantise, decay, partial dot products along the row
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
+          const uint32_t w[4] = {cw.x ^ 0x80808080u, cw.y ^ 0x80808080u, cw.z ^ 0x80808080u, cw.w ^ 0x80808080u};
+          const float2 s2 = splat(srow[i]);
+          float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            const float2 e = mul2(mul2(s8x2_to_float<0, 2>(w[m]), s2), alpha2);
+            const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
+            hE[i][m] = e; hO[i][m] = o;
+            ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
+            aq = fma2(e, qE[m], aq); aq = fma2(o, qO[m], aq);
+          }
+          dk[i] = ak.x + ak.y; dq[i] = aq.x + aq.y;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { dk[i] = warp_sum8(dk[i]); dq[i] = warp_sum8(dq[i]); }
+
+        // phase 2: rank-1 write, add the residual, row maxima
+        float amax[4], oval[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float dv = __fmul_rn(beta, __fadd_rn(vrow[i], -dk[i]));
+          oval[i] = fmaf(dv, kq, dq[i]);
+          const float2 dv2 = splat(dv);
+          const float es = (RSCALE == CARRY_SCALE_PER_V) ? rscale[r0 + i] : es_head;
+          float am = 0.f;
+          if constexpr (RES == CARRY_RES_INT4) {
+            const uint2 rw = *reinterpret_cast<const uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2);
+            const uint32_t w[2] = {rw.x ^ 0x88888888u, rw.y ^ 0x88888888u};
+            const float2 es2 = splat(es), es16 = splat(es * 0.0625f);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              float2 lo, hi;
+              if (m & 1) s4x4_to_float<2, 3>(w[m >> 1], lo, hi); else s4x4_to_float<0, 1>(w[m >> 1], lo, hi);
+              const float2 te = add2(add2(hE[i][m], mul2(kE[m], dv2)), mul2(lo, es2));
+              const float2 to = add2(add2(hO[i][m], mul2(kO[m], dv2)), mul2(hi, es16));
+              hE[i][m] = te; hO[i][m] = to;
+              am = max3abs(max3abs(am, te), to);
+            }
+          } else {
+            const uint4 rw = *reinterpret_cast<const uint4*>(sb + L::kResid + (r0 + i) * kT + c0);
+            const uint32_t w[4] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u, rw.z ^ 0x80808080u, rw.w ^ 0x80808080u};
+            const float2 es2 = splat(es);
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              const float2 te = add2(add2(hE[i][m], mul2(kE[m], dv2)), mul2(s8x2_to_float<0, 2>(w[m]), es2));
+              const float2 to = add2(add2(hO[i][m], mul2(kO[m], dv2)), mul2(s8x2_to_float<1, 3>(w[m]), es2));
+              hE[i][m] = te; hO[i][m] = to;
+              am = max3abs(max3abs(am, te), to);
+            }
+          }
+          amax[i] = am;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) amax[i] = warp_max8(amax[i]);
+        if (cg == 0) {                      // four consecutive outputs of this lane's rows
+          if (p.o_dtype == CARRY_F32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_off + r0) =
+                make_float4(oval[0], oval[1], oval[2], oval[3]);
+          } else if (p.o_dtype == CARRY_BF16) {
+            const __nv_bfloat162 a = __floats2bfloat162_rn(oval[0], oval[1]), b = __floats2bfloat162_rn(oval[2], oval[3]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off + r0) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+          } else {
+            const __half2 a = __floats2half2_rn(oval[0], oval[1]), b = __floats2half2_rn(oval[2], oval[3]);
+            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + out_off + r0) =
+                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+          }
+        }
+
+        // new state scales: lane cg of a row group does row cg's divisions, then they are shared
+        float snew[4], sinv[4];
+        {
+          const float mine = (cg == 0) ? amax[0] : (cg == 1) ? amax[1] : (cg == 2) ? amax[2] : amax[3];
+          const float s_mine = scale_from_amax(mine, p.qmax, p.eps_mode);
+          const float i_mine = __frcp_rn(s_mine);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
+            sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
+          }
+        }
+
+        // phase 3: state codes, new residual
+        float eamax[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 inv2 = splat(sinv[i]), ns2 = splat(-snew[i]);
+          float2 yE[4], yO[4];
+          float em = 0.f;
+#pragma unroll
+          for (int m = 0; m < 4; ++m) {
+            yE[m] = add2(mul2(hE[i][m], inv2), magic2);
+            yO[m] = add2(mul2(hO[i][m], inv2), magic2);
+            hE[i][m] = add2(hE[i][m], mul2(add2(yE[m], nmagic2), ns2));
+            hO[i][m] = add2(hO[i][m], mul2(add2(yO[m], nmagic2), ns2));
+            em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
+          }
+          const float thr = snew[i] * kTieGuard;
+          if (em > thr) {                    // rare: a quotient within the tie guard somewhere in these 16
+            em = 0.f;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              redecide(hE[i][m].x, yE[m].x, snew[i], thr); redecide(hE[i][m].y, yE[m].y, snew[i], thr);
+              redecide(hO[i][m].x, yO[m].x, snew[i], thr); redecide(hO[i][m].y, yO[m].y, snew[i], thr);
+              em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
+            }
+          }
+          uint32_t packed[4];
+#pragma unroll
+          for (int m = 0; m < 4; ++m)
+            packed[m] = pack4(__float_as_uint(yE[m].x), __float_as_uint(yO[m].x), __float_as_uint(yE[m].y),
+                              __float_as_uint(yO[m].y));
+          *reinterpret_cast<uint4*>(sb + L::kCodes + (r0 + i) * kT + c0) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          eamax[i] = em;
+        }
+
+        // phase 4: residual scale and codes
+        float esn[4], einv[4];
+        if constexpr (RSCALE == CARRY_SCALE_PER_V) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) eamax[i] = warp_max8(eamax[i]);
+          const float mine = (cg == 0) ? eamax[0] : (cg == 1) ? eamax[1] : (cg == 2) ? eamax[2] : eamax[3];
+          const float s_mine = scale_from_amax(mine, rqmax, p.eps_mode);
+          const float i_mine = __frcp_rn(s_mine);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            esn[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
+            einv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
+          }
+        } else {
+          const float m4 = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
+          if (lane == 0) head_red[it & 1][warp] = m4;
+          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          float m = head_red[it & 1][0];
+#pragma unroll
+          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
+          const float e1 = scale_from_amax(m, rqmax, p.eps_mode);
+          const float i1 = __frcp_rn(e1);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { esn[i] = e1; einv[i] = i1; }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 invE = splat(einv[i]);
+          if constexpr (RES == CARRY_RES_INT4) {
+            // even columns: rint(e/es) + 8 + 128 lands in the low mantissa bits; 16 * rint(e/es) of the odd
+            // column is added on top, so the low byte of the sum is (odd + 8) << 4 | (even + 8); the final
+            // XOR removes the bias of both nibbles.
+            const float2 mE = splat(kMagicRound + 136.0f), sixteen = splat(16.0f);
+            uint32_t by[8];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              const float2 ye = add2(mul2(hE[i][m], invE), mE);
+              const float2 co = add2(add2(mul2(hO[i][m], invE), magic2), nmagic2);
+              const float2 pk = fma2(co, sixteen, ye);
+              by[2 * m] = __float_as_uint(pk.x);
+              by[2 * m + 1] = __float_as_uint(pk.y);
+            }
+            const uint32_t w0 = pack4(by[0], by[1], by[2], by[3]) ^ 0x88888888u;
+            const uint32_t w1 = pack4(by[4], by[5], by[6], by[7]) ^ 0x88888888u;
+            *reinterpret_cast<uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2) = make_uint2(w0, w1);
+          } else {
+            uint32_t packed[4];
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+              const float2 ye = add2(mul2(hE[i][m], invE), magic2);
+              const float2 yo = add2(mul2(hO[i][m], invE), magic2);
+              packed[m] = pack4(__float_as_uint(ye.x), __float_as_uint(yo.x), __float_as_uint(ye.y),
+                                __float_as_uint(yo.y));
+            }
+            *reinterpret_cast<uint4*>(sb + L::kResid + (r0 + i) * kT + c0) =
+                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+          }
+        }
+        if (cg == 0) {
+          *reinterpret_cast<float4*>(sb + L::kSScale + r0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
+          if (RSCALE == CARRY_SCALE_PER_V)
+            *reinterpret_cast<float4*>(sb + L::kRScale + r0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
+        }
+        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) {
+          float* dst = p.packed ? p.rscale_out + (long long)slot * p.stride_rscale_slot + hv
+                                : p.rscale_out + (long long)n * p.HV + hv;
+          *dst = esn[0];
+        }
+      } else {
+        // ---------------- statequant layout [K][V]: lane = 4 columns x 16 rows ----
+        // columns {c0, c0+1} are held as pair A, {c0+2, c0+3} as pair B
+        const int r0 = 16 * warp, c0 = 4 * lane;
+        float* red_dot = col_red;                       // [warp][col][2]
+        float* red_max = col_red + kWarps * kT * 2;     // [warp][col]
+        float* red_emax = red_max + kWarps * kT;        // [warp][col]
+        float kq;
+        {
+          const float4 k4 = act4<QDT>(sb + L::kK, 4 * lane), q4 = act4<QDT>(sb + L::kQ, 4 * lane);
+          kq = warp_sum32(fmaf(k4.x, q4.x, fmaf(k4.y, q4.y, fmaf(k4.z, q4.z, k4.w * q4.w)))) * (k_mul * q_mul);
+        }
+        float krow[16], qrow[16];            // k and q of this warp's 16 rows (the same in every lane)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float4 k4 = act4<QDT>(sb + L::kK, r0 + 4 * i), q4 = act4<QDT>(sb + L::kQ, r0 + 4 * i);
+          krow[4 * i] = k4.x * k_mul; krow[4 * i + 1] = k4.y * k_mul; krow[4 * i + 2] = k4.z * k_mul; krow[4 * i + 3] = k4.w * k_mul;
+          qrow[4 * i] = q4.x * q_mul; qrow[4 * i + 1] = q4.y * q_mul; qrow[4 * i + 2] = q4.z * q_mul; qrow[4 * i + 3] = q4.w * q_mul;
+        }
+        float scol[4];
+        {
+          const float4 s4 = *reinterpret_cast<const float4*>(sscale + c0);
+          scol[0] = s4.x; scol[1] = s4.y; scol[2] = s4.z; scol[3] = s4.w;
+        }
+        const float2 sA = make_float2(scol[0], scol[1]), sB = make_float2(scol[2], scol[3]);
+        float2 hA[16], hB[16];
+        float2 dkA = make_float2(0.f, 0.f), dkB = dkA, dqA = dkA, dqB = dkA;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const uint32_t w = *reinterpret_cast<const uint32_t*>(sb + L::kCodes + (r0 + i) * kT + c0) ^ 0x80808080u;
+          const float2 a = mul2(mul2(s8x2_to_float<0, 1>(w), sA), alpha2);
+          const float2 b = mul2(mul2(s8x2_to_float<2, 3>(w), sB), alpha2);
+          hA[i] = a; hB[i] = b;
+          const float2 kr = splat(krow[i]), qr = splat(qrow[i]);
+          dkA = fma2(a, kr, dkA); dkB = fma2(b, kr, dkB);
+          dqA = fma2(a, qr, dqA); dqB = fma2(b, qr, dqB);
+        }
+        // finish the column sums across the 8 warps
+        float dk[4], dq[4];
+        {
+          float4* dst = reinterpret_cast<float4*>(red_dot + ((size_t)warp * kT + c0) * 2);
+          dst[0] = make_float4(dkA.x, dqA.x, dkA.y, dqA.y);
+          dst[1] = make_float4(dkB.x, dqB.x, dkB.y, dqB.y);
+          warps_meet(&meet_bar[0], meet_parity, lane, poison, p.status);
+#pragma unroll
+          for (int b = 0; b < 4; ++b) { dk[b] = 0.f; dq[b] = 0.f; }
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            const float4* src = reinterpret_cast<const float4*>(red_dot + ((size_t)w * kT + c0) * 2);
+            const float4 x0 = src[0], x1 = src[1];
+            dk[0] += x0.x; dq[0] += x0.y; dk[1] += x0.z; dq[1] += x0.w;
+            dk[2] += x1.x; dq[2] += x1.y; dk[3] += x1.z; dq[3] += x1.w;
+          }
+        }
+        float dv[4], oval[4], es_col[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          dv[b] = __fmul_rn(beta, __fadd_rn(act<QDT>(sb + L::kV, c0 + b), -dk[b]));
+          oval[b] = fmaf(dv[b], kq, dq[b]);
+          es_col[b] = (RSCALE == CARRY_SCALE_PER_V) ? rscale[c0 + b] : es_head;
+        }
+        const float2 dvA = make_float2(dv[0], dv[1]), dvB = make_float2(dv[2], dv[3]);
+        float amax[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          float2 eA, eB;
+          if constexpr (RES == CARRY_RES_INT4) {
+            const uint32_t w =
+                (uint32_t)(*reinterpret_cast<const uint16_t*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2)) ^ 0x8888u;
+            float2 lo, hi;                              // lo = cols {c0, c0+2}, hi = 16 * cols {c0+1, c0+3}
+            s4x4_to_float<0, 1>(w, lo, hi);
+            eA = mul2(make_float2(lo.x, hi.x), make_float2(es_col[0], es_col[1] * 0.0625f));
+            eB = mul2(make_float2(lo.y, hi.y), make_float2(es_col[2], es_col[3] * 0.0625f));
+          } else {
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(sb + L::kResid + (r0 + i) * kT + c0) ^ 0x80808080u;
+            eA = mul2(s8x2_to_float<0, 1>(w), make_float2(es_col[0], es_col[1]));
+            eB = mul2(s8x2_to_float<2, 3>(w), make_float2(es_col[2], es_col[3]));
+          }
+          const float2 kr = splat(krow[i]);
+          const float2 tA = add2(add2(hA[i], mul2(kr, dvA)), eA);
+          const float2 tB = add2(add2(hB[i], mul2(kr, dvB)), eB);
+          hA[i] = tA; hB[i] = tB;
+          amax[0] = fmaxf(amax[0], fabsf(tA.x)); amax[1] = fmaxf(amax[1], fabsf(tA.y));
+          amax[2] = fmaxf(amax[2], fabsf(tB.x)); amax[3] = fmaxf(amax[3], fabsf(tB.y));
+        }
+        if (warp == 0) {
+#pragma unroll
+          for (int b = 0; b < 4; ++b) store_from_float(p.out, out_off + c0 + b, p.o_dtype, oval[b]);
+        }
+        *reinterpret_cast<float4*>(red_max + (size_t)warp * kT + c0) = make_float4(amax[0], amax[1], amax[2], amax[3]);
+        warps_meet(&meet_bar[1], meet_parity, lane, poison, p.status);
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) {
+          const float4 x = *reinterpret_cast<const float4*>(red_max + (size_t)w * kT + c0);
+          amax[0] = fmaxf(amax[0], x.x); amax[1] = fmaxf(amax[1], x.y);
+          amax[2] = fmaxf(amax[2], x.z); amax[3] = fmaxf(amax[3], x.w);
+        }
+        float snew[4], thr[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) { snew[b] = scale_from_amax(amax[b], p.qmax, p.eps_mode); thr[b] = snew[b] * kTieGuard; }
+        const float2 invA = make_float2(__frcp_rn(snew[0]), __frcp_rn(snew[1]));
+        const float2 invB = make_float2(__frcp_rn(snew[2]), __frcp_rn(snew[3]));
+        const float2 nsA = make_float2(-snew[0], -snew[1]), nsB = make_float2(-snew[2], -snew[3]);
+        float eamax[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t cw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 yA = add2(mul2(hA[i], invA), magic2), yB = add2(mul2(hB[i], invB), magic2);
+          hA[i] = add2(hA[i], mul2(add2(yA, nmagic2), nsA));
+          hB[i] = add2(hB[i], mul2(add2(yB, nmagic2), nsB));
+          cw[i] = pack4(__float_as_uint(yA.x), __float_as_uint(yA.y), __float_as_uint(yB.x), __float_as_uint(yB.y));
+          eamax[0] = fmaxf(eamax[0], fabsf(hA[i].x)); eamax[1] = fmaxf(eamax[1], fabsf(hA[i].y));
+          eamax[2] = fmaxf(eamax[2], fabsf(hB[i].x)); eamax[3] = fmaxf(eamax[3], fabsf(hB[i].y));
+        }
+        if (fmaxf(fmaxf(eamax[0] - thr[0], eamax[1] - thr[1]), fmaxf(eamax[2] - thr[2], eamax[3] - thr[3])) > 0.f) {
+          eamax[0] = eamax[1] = eamax[2] = eamax[3] = 0.f;      // rare: a quotient within the tie guard
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float2 yA = add2(s8x2_to_float<0, 1>(cw[i] ^ 0x80808080u), magic2);
+            float2 yB = add2(s8x2_to_float<2, 3>(cw[i] ^ 0x80808080u), magic2);
+            redecide(hA[i].x, yA.x, snew[0], thr[0]); redecide(hA[i].y, yA.y, snew[1], thr[1]);
+            redecide(hB[i].x, yB.x, snew[2], thr[2]); redecide(hB[i].y, yB.y, snew[3], thr[3]);
+            cw[i] = pack4(__float_as_uint(yA.x), __float_as_uint(yA.y), __float_as_uint(yB.x), __float_as_uint(yB.y));
+            eamax[0] = fmaxf(eamax[0], fabsf(hA[i].x)); eamax[1] = fmaxf(eamax[1], fabsf(hA[i].y));
+            eamax[2] = fmaxf(eamax[2], fabsf(hB[i].x)); eamax[3] = fmaxf(eamax[3], fabsf(hB[i].y));
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(sb + L::kCodes + (r0 + i) * kT + c0) = cw[i];
+        float esn[4];
+        if constexpr (RSCALE == CARRY_SCALE_PER_V) {
+          *reinterpret_cast<float4*>(red_emax + (size_t)warp * kT + c0) =
+              make_float4(eamax[0], eamax[1], eamax[2], eamax[3]);
+          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+#pragma unroll
+          for (int w = 0; w < kWarps; ++w) {
+            const float4 x = *reinterpret_cast<const float4*>(red_emax + (size_t)w * kT + c0);
+            eamax[0] = fmaxf(eamax[0], x.x); eamax[1] = fmaxf(eamax[1], x.y);
+            eamax[2] = fmaxf(eamax[2], x.z); eamax[3] = fmaxf(eamax[3], x.w);
+          }
+#pragma unroll
+          for (int b = 0; b < 4; ++b) esn[b] = scale_from_amax(eamax[b], rqmax, p.eps_mode);
+        } else {
+          float m = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
+          if (lane == 0) head_red[it & 1][warp] = m;
+          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          m = head_red[it & 1][0];
+#pragma unroll
+          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
+          esn[0] = esn[1] = esn[2] = esn[3] = scale_from_amax(m, rqmax, p.eps_mode);
+        }
+        const float2 ieA = make_float2(__frcp_rn(esn[0]), __frcp_rn(esn[1]));
+        const float2 ieB = make_float2(__frcp_rn(esn[2]), __frcp_rn(esn[3]));
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float2 rA = add2(mul2(hA[i], ieA), magic2), rB = add2(mul2(hB[i], ieB), magic2);
+          const uint32_t y0 = __float_as_uint(rA.x), y1 = __float_as_uint(rA.y);
+          const uint32_t y2 = __float_as_uint(rB.x), y3 = __float_as_uint(rB.y);
+          if constexpr (RES == CARRY_RES_INT4) {
+            const uint32_t v16 = (y0 & 0xFu) | ((y1 & 0xFu) << 4) | ((y2 & 0xFu) << 8) | ((y3 & 0xFu) << 12);
+            *reinterpret_cast<uint16_t*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2) = (uint16_t)v16;
+          } else {
+            *reinterpret_cast<uint32_t*>(sb + L::kResid + (r0 + i) * kT + c0) = pack4(y0, y1, y2, y3);
+          }
+        }
+        // scales: every warp holds all 128 of them; warp w publishes its 16-column share
+        // (columns 16w..16w+15 are held by lanes 4w..4w+3)
+        if ((lane >> 2) == warp) {
+          *reinterpret_cast<float4*>(sb + L::kSScale + c0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
+          if (RSCALE == CARRY_SCALE_PER_V)
+            *reinterpret_cast<float4*>(sb + L::kRScale + c0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
+        }
+        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) p.rscale_out[(long long)n * p.HV + hv] = esn[0];
+      }
+    }
+    if (live) meet_parity ^= 1u;
+
+    // ---- this warp's 16 rows go back; free the previous stage; refill it ---------
+    __syncwarp();
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      if (live && !*poison) {
+        int8_t* codes_out;
+        uint8_t* resid_out;
+        float *ss_out, *rs_out;
+        if (p.packed) {
+          codes_out = p.codes_out + (long long)slot * p.stride_state_slot + (long long)hv * kT * kT;
+          resid_out = reinterpret_cast<uint8_t*>(p.resid_out) + (long long)slot * p.stride_resid_slot +
+                      (long long)hv * L::kResidBytes;
+          ss_out = p.sscale_out + (long long)slot * p.stride_sscale_slot + (long long)hv * kT;
+          rs_out = p.rscale_out + (long long)slot * p.stride_rscale_slot + (long long)hv * kT;
+        } else {
+          const long long nh = (long long)n * p.HV + hv;
+          codes_out = p.codes_out + nh * kT * kT;
+          resid_out = reinterpret_cast<uint8_t*>(p.resid_out) + nh * L::kResidBytes;
+          ss_out = p.sscale_out + nh * kT;
+          rs_out = p.rscale_out + nh * kT;
+        }
+        constexpr int kRowsB = 16 * kT;                       // bytes of 16 rows of codes
+        constexpr int kResRowsB = L::kResidBytes / kWarps;    // bytes of 16 rows of residual
+        bulk_store(codes_out + warp * kRowsB, sb + L::kCodes + warp * kRowsB, kRowsB);
+        bulk_store(resid_out + warp * kResRowsB, sb + L::kResid + warp * kResRowsB, kResRowsB);
+        bulk_store(ss_out + warp * 16, sb + L::kSScale + warp * 64, 64);
+        if (RSCALE == CARRY_SCALE_PER_V) bulk_store(rs_out + warp * 16, sb + L::kRScale + warp * 64, 64);
+      }
+      bulk_commit();
+      // Stage (it-1) % S is free once every warp's stores of tile it-1 have left
+      // shared memory.  The warp that observes this last refills the stage, so
+      // nobody waits here.
+      if (it > 0 && it - 1 + S < my_tiles) {
+        bulk_wait_read<1>();
+        __threadfence_block();
+        const int prev = (it - 1) % S;
+        if (atomicAdd(&done_cnt[prev], 1) == kWarps - 1) {
+          __threadfence_block();
+          done_cnt[prev] = 0;
+          if (!*poison) issue_tile<LAYOUT, RES, RSCALE>(p, smem, full_bar, slot_cache, it - 1 + S);
+        }
+      }
+    }
+  }
+  if (lane == 0) bulk_wait_read<0>();
+  __syncthreads();
+}
+
+template <int LAYOUT, int RES, int RSCALE, int QDT>
+int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
+  using L = StageLayout<RES, LAYOUT>;
+  auto kern = gdn_tile128_kernel<LAYOUT, RES, RSCALE, QDT>;
+  const size_t smem = (size_t)L::kBytes * L::kStages;
+  static thread_local bool configured[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return CARRY_GDN_ERR_NO_DEVICE;
+  if (dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return CARRY_GDN_ERR_NO_DEVICE;
+    }
+    configured[dev] = true;
+  }
+  const long long tiles = (long long)p.B * p.HV;
+  const long long ctas = (long long)L::kCtasPerSm * sms;
+  const int grid = (int)(tiles < ctas ? tiles : ctas);
+  kern<<<grid, kThreads, smem, stream>>>(p);
+  return cudaGetLastError() == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
+}
+
+template <int LAYOUT, int RES, int RSCALE>
+int launch_dtype(const KParams& p, cudaStream_t stream, int sms) {
+  if (p.qkv_dtype == CARRY_F32) return launch_variant<LAYOUT, RES, RSCALE, CARRY_F32>(p, stream, sms);
+  if (p.qkv_dtype == CARRY_BF16) return launch_variant<LAYOUT, RES, RSCALE, CARRY_BF16>(p, stream, sms);
+  return launch_variant<LAYOUT, RES, RSCALE, CARRY_F16>(p, stream, sms);
+}
+
+// all variants of one memory layout
+template <int LAYOUT>
+int launch_layout(const KParams& p, cudaStream_t stream, int sms) {
+  const bool i4 = p.res_fmt == CARRY_RES_INT4, pv = p.rscale_mode == CARRY_SCALE_PER_V;
+  if (i4) return pv ? launch_dtype<LAYOUT, CARRY_RES_INT4, CARRY_SCALE_PER_V>(p, stream, sms)
+                    : launch_dtype<LAYOUT, CARRY_RES_INT4, CARRY_SCALE_PER_HEAD>(p, stream, sms);
+  return pv ? launch_dtype<LAYOUT, CARRY_RES_INT8, CARRY_SCALE_PER_V>(p, stream, sms)
+            : launch_dtype<LAYOUT, CARRY_RES_INT8, CARRY_SCALE_PER_HEAD>(p, stream, sms);
+}
+
+}  // namespace
+}  // namespace carry
