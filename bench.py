@@ -71,6 +71,8 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=BATCH, help="requests per GPU per step")
     ap.add_argument("--layers", type=int, default=LAYERS)
     ap.add_argument("--resid", choices=["int4", "int8"], default="int4")
+    ap.add_argument("--resid-scale", choices=["head", "v"], default="head",
+                    help="one residual scale per head (the named workload) or per V row")
     ap.add_argument("--warm-steps", type=int, default=WARM_STEPS,
                     help="untimed steps that build the initial state (64 = the named workload)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -95,7 +97,7 @@ def peak_hbm():
 class Workload:
     """Per-GPU state and inputs of the decode step, resident in HBM."""
 
-    def __init__(self, device, batch, layers, resid, seed):
+    def __init__(self, device, batch, layers, resid, seed, resid_scale="head"):
         from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
         self.qpd, self.device, self.batch, self.layers = qpd, device, batch, layers
         self.resid_fmt = qpd.RESID_INT4 if resid == "int4" else qpd.RESID_INT8
@@ -106,7 +108,7 @@ class Workload:
         self.pools, self.indices, self.mixed, self.a, self.b, self.out = [], [], [], [], [], []
         for _ in range(layers):
             self.pools.append(qpd.init_quantized_state(slots, HV, V, K, device,
-                                                       resid_fmt=self.resid_fmt, resid_scale="head"))
+                                                       resid_fmt=self.resid_fmt, resid_scale=resid_scale))
             self.indices.append((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32).to(device))
             self.mixed.append(torch.randn(batch, width, generator=g).to(torch.bfloat16).to(device))
             self.a.append(torch.randn(batch, HV, generator=g).to(torch.bfloat16).to(device))
@@ -249,7 +251,7 @@ def e2e_run(wl, steps, warmup):
 # CPU arm: the oracle port, timed on the host cores; doubles as the checker
 # ---------------------------------------------------------------------------
 
-def cpu_sample_inputs(batch, layers, resid, seed=1234):
+def cpu_sample_inputs(batch, layers, resid, seed=1234, resid_scale="head"):
     """CPU copy of a bounded sample of the workload (same shapes and laws)."""
     from oracle import gdn_oracle as orc
     g = torch.Generator().manual_seed(seed)
@@ -258,7 +260,7 @@ def cpu_sample_inputs(batch, layers, resid, seed=1234):
     sample = []
     for _ in range(layers):
         pool = torch.randn(batch + 1, HV, V, K, generator=g) * 0.124
-        st = list(orc.init_quantized_pool(batch + 1, HV, V, K, h0=pool, resid_fmt=fmt, resid_scale="head"))
+        st = list(orc.init_quantized_pool(batch + 1, HV, V, K, h0=pool, resid_fmt=fmt, resid_scale=resid_scale))
         idx = (torch.randperm(batch, generator=g) + 1).to(torch.int32)
         mixed = torch.randn(batch, width, generator=g).to(torch.bfloat16)
         a = torch.randn(batch, HV, generator=g).to(torch.bfloat16)
@@ -280,10 +282,10 @@ def cpu_oracle_pass(sample, fmt):
     return outs
 
 
-def time_cpu_oracle(batch, layers, resid, passes, warm=1):
+def time_cpu_oracle(batch, layers, resid, passes, warm=1, resid_scale="head"):
     """Seconds per pass of the oracle over the sample (all host threads)."""
     torch.set_num_threads(os.cpu_count() or 1)
-    sample, fmt = cpu_sample_inputs(batch, layers, resid)
+    sample, fmt = cpu_sample_inputs(batch, layers, resid, resid_scale=resid_scale)
     for _ in range(warm):
         cpu_oracle_pass(sample, fmt)
     times = []
@@ -294,14 +296,14 @@ def time_cpu_oracle(batch, layers, resid, passes, warm=1):
     return sum(times) / len(times), batch * layers
 
 
-def cpu_baseline_and_parity(wl, resid):
+def cpu_baseline_and_parity(wl, resid, resid_scale="head"):
     """Time the oracle on a bounded sample and, on that same sample, check the
     GPU step against it (validate before timing)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle import gdn_oracle as orc
     import parity
     s_batch, s_layers = min(wl.batch, 16), 2
-    sample, fmt = cpu_sample_inputs(s_batch, s_layers, resid)
+    sample, fmt = cpu_sample_inputs(s_batch, s_layers, resid, resid_scale=resid_scale)
     # GPU result on the sample (teacher-forced from the same start state)
     dev = wl.device
     f_state = f_resid = 0.0
@@ -323,7 +325,7 @@ def cpu_baseline_and_parity(wl, resid):
         f_state, f_resid = max(f_state, fs), max(f_resid, fr)
     # timing: enough passes for roughly 10-20 s of CPU work
     passes = max(2, min(20, int(12.0 / max(first, 1e-3))))
-    sec, units = time_cpu_oracle(s_batch, s_layers, resid, passes, warm=0)
+    sec, units = time_cpu_oracle(s_batch, s_layers, resid, passes, warm=0, resid_scale=resid_scale)
     return ({"value": units / sec, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
              "sample": f"{s_layers} layers x {s_batch} requests of the same workload "
                        f"({units} slot-layer-steps per pass, {passes} passes, torch CPU oracle)"},
@@ -362,10 +364,12 @@ def run_reference_arm(args, rank):
 def workload_config(args, batch, layers, note=None):
     cfg = {"workload": "slot-indexed GDN decode step: int8 state + packed int4 residual (per-head "
                        "residual scale), 24 layers x 64 requests per GPU, pools of 256 slots"
-                       if (args.resid == "int4" and batch == BATCH and layers == LAYERS) else
+                       if (args.resid == "int4" and args.resid_scale == "head" and batch == BATCH
+                           and layers == LAYERS) else
                        f"slot-indexed GDN decode step, {args.resid} residual",
            "requests_per_gpu": batch, "layers": layers, "H": H, "HV": HV, "K": K, "V": V,
-           "pool_slots": POOL_SLOTS, "resid": args.resid, "resid_scale": "per-head",
+           "pool_slots": POOL_SLOTS, "resid": args.resid,
+           "resid_scale": "per-head" if args.resid_scale == "head" else "per-V",
            "activations": "bf16", "parallelism": f"slot-sharded x{args.gpus}, no collective",
            "l2": "inputs larger than L2: each step touches a different 52 MB of state per layer, "
                  "1.26 GB per step against 126 MB of L2"}
@@ -401,13 +405,14 @@ def main():
     from carrykernel_b200 import _lib
     lib = _lib.load_library()
 
-    wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank)
+    wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank,
+                  resid_scale=args.resid_scale)
     wl.warm_state(args.warm_steps)
     kernel_used = lib.carry_gdn_last_kernel()
 
     cpu_base = parity_stats = None
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
-        cpu_base, parity_stats = cpu_baseline_and_parity(wl, args.resid)
+        cpu_base, parity_stats = cpu_baseline_and_parity(wl, args.resid, args.resid_scale)
 
     # capture one decode step (all layers) in a CUDA graph
     side = torch.cuda.Stream(device)
