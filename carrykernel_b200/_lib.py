@@ -87,7 +87,7 @@ def load_library(path: str | None = None):
     with _lock:
         if _lib is not None:
             return _lib
-        path = path or LIB_PATH
+        path = path or os.environ.get("CARRY_GDN_LIBRARY") or LIB_PATH
         if not os.path.exists(path):
             raise CudaUnavailable(
                 f"{path} is missing: build it with `python -m carrykernel_b200._build`")

@@ -135,6 +135,10 @@ int carry_gdn_packed_decode(const CarryGdnPackedArgs* a, void* stream) {
   p.slot_idx = a->ssm_state_indices; p.stride_idx = a->stride_indices;
   p.num_slots = a->num_slots;
   p.out = a->out;
+#ifdef CARRY_PROFILE
+  p.prof = reinterpret_cast<long long*>(a->status);   // debug builds reuse the status pointer (8 x int64)
+  p.status = nullptr;
+#endif
   return dispatch(p, static_cast<cudaStream_t>(stream));
 }
 

@@ -384,6 +384,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
   uint32_t meet_parity = 0;            // flips once per computed tile
 
+#ifdef CARRY_PROFILE
+  long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
+  long long prof_t = clock64();
+#define PROF_MARK(k) { const long long now_ = clock64(); prof_acc[k] += now_ - prof_t; prof_t = now_; }
+#else
+#define PROF_MARK(k)
+#endif
   for (int it = 0; it < my_tiles; ++it) {
     const int s = it % S;
     const uint32_t parity = (uint32_t)(it / S) & 1u;
@@ -392,6 +399,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const int n = tile / p.HV, hv = tile - n * p.HV;
 
     mbar_wait(&full_bar[s], parity, poison, p.status);
+#ifdef CARRY_PROFILE
+    if (blockIdx.x == 0 && tid == 0 && p.prof && it < 64) p.prof[16 + it] = clock64() - prof_t;
+#endif
+    PROF_MARK(0)
     const int slot = *reinterpret_cast<volatile int*>(sb + L::kHeader);
     const long long out_off = ((long long)n * p.HV + hv) * kT;
     const bool live = slot > 0 && !*poison;
@@ -461,8 +472,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
           dk[i] = ak.x + ak.y; dq[i] = aq.x + aq.y;
         }
+        PROF_MARK(1)
 #pragma unroll
         for (int i = 0; i < 4; ++i) { dk[i] = warp_sum8(dk[i]); dq[i] = warp_sum8(dq[i]); }
+        PROF_MARK(2)
 
         // phase 2: rank-1 write, add the residual, row maxima
         float amax[4], oval[4];
@@ -530,6 +543,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
 
+        PROF_MARK(3)
         // phase 3: state codes, new residual
         float eamax[4];
 #pragma unroll
@@ -565,6 +579,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           eamax[i] = em;
         }
 
+        PROF_MARK(4)
         // phase 4: residual scale and codes
         float esn[4], einv[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
@@ -582,6 +597,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           const float m4 = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
           if (lane == 0) head_red[it & 1][warp] = m4;
           warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          PROF_MARK(5)
           float m = head_red[it & 1][0];
 #pragma unroll
           for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
@@ -809,11 +825,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       }
     }
     if (live) meet_parity ^= 1u;
+    PROF_MARK(6)
 
     // ---- this warp's 16 rows go back; free the previous stage; refill it ---------
     __syncwarp();
     fence_async_smem();
     __syncwarp();
+    PROF_MARK(7)
     if (lane == 0) {
       if (live && !*poison) {
         int8_t* codes_out;
@@ -840,11 +858,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         if (RSCALE == CARRY_SCALE_PER_V) bulk_store(rs_out + warp * 16, sb + L::kRScale + warp * 64, 64);
       }
       bulk_commit();
+      PROF_MARK(8)
       // Stage (it-1) % S is free once every warp's stores of tile it-1 have left
       // shared memory.  The warp that observes this last refills the stage, so
       // nobody waits here.
       if (it > 0 && it - 1 + S < my_tiles) {
         bulk_wait_read<1>();
+        PROF_MARK(9)
         __threadfence_block();
         const int prev = (it - 1) % S;
         if (atomicAdd(&done_cnt[prev], 1) == kWarps - 1) {
@@ -854,7 +874,15 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
       }
     }
+    PROF_MARK(10)
+    __syncwarp();
+    PROF_MARK(11)
   }
+#ifdef CARRY_PROFILE
+  if (lane == 0 && p.prof) {
+    for (int k = 0; k < 12; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.prof) + k, (unsigned long long)prof_acc[k]);
+  }
+#endif
   if (lane == 0) bulk_wait_read<0>();
   __syncthreads();
 }
