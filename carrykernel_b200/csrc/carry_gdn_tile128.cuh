@@ -40,7 +40,7 @@ constexpr int kT = 128;                 // tile edge
 constexpr int kThreads = 256;
 constexpr int kWarps = 8;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kTileCache = 128;         // per-CTA cache of slot ids and gates for its first tiles
+constexpr int kTileCache = 64;         // per-CTA cache of slot ids and gates for its first tiles
 
 enum { LAYOUT_VK = 0, LAYOUT_KV = 1 };  // slot layout [V][K]; statequant layout [K][V]
 
@@ -177,23 +177,33 @@ __device__ __forceinline__ float warp_max32(float x) {
 // ---------------------------------------------------------------------------
 // shared-memory stage layout (bytes)
 // ---------------------------------------------------------------------------
-template <int RES, int LAYOUT = 0>
+// Static shared memory next to the stage ring: barriers, the per-CTA tile caches,
+// the per-warp q scratch (slot layout) or the column-reduction space (statequant
+// layout).  Upper bounds, used to size the ring.
+constexpr int kStaticVK = 7168;
+constexpr int kStaticKV = 19456;
+constexpr int kSmemPerCta2 = 115712;    // (228 KB - 2 x 1 KB reserved) / 2: two CTAs per SM
+constexpr int kSmemPerCta1 = 231424;    // one CTA per SM
+
+template <int RES, int LAYOUT, int QDT>
 struct StageLayout {
+  static constexpr int kVecBytes = kT * (QDT == CARRY_F32 ? 4 : 2);
   static constexpr int kResidBytes = (RES == CARRY_RES_INT4) ? kT * kT / 2 : kT * kT;
   static constexpr int kCodes = 0;
   static constexpr int kResid = kT * kT;
   static constexpr int kSScale = kResid + kResidBytes;       // 128 floats
   static constexpr int kRScale = kSScale + 512;              // 128 floats (per V) or a row of per-head scales
-  static constexpr int kQ = kRScale + 512;                   // raw q, up to 128 x 4 B
-  static constexpr int kK = kQ + 512;
-  static constexpr int kV = kK + 512;
-  static constexpr int kHeader = kV + 512;                   // int slot
+  static constexpr int kQ = kRScale + 512;                   // raw q, k, v of this head
+  static constexpr int kK = kQ + kVecBytes;
+  static constexpr int kV = kK + kVecBytes;
+  static constexpr int kHeader = kV + kVecBytes;             // int slot
   static constexpr int kBytes = kHeader + 16;
-  // slot layout: two CTAs per SM; the statequant layout also needs 16 KB of
-  // cross-warp reduction space, so its int8-residual variant runs one CTA per SM
-  static constexpr int kCtasPerSm = (LAYOUT == 1 && RES != CARRY_RES_INT4) ? 1 : 2;
-  static constexpr int kStages = (LAYOUT == 0) ? ((RES == CARRY_RES_INT4) ? 4 : 3)
-                                               : ((RES == CARRY_RES_INT4) ? 3 : 5);
+  static constexpr int kStatic = (LAYOUT == 0) ? kStaticVK : kStaticKV;
+  // two CTAs per SM when at least 3 stages fit next to the static part, else one
+  static constexpr int kCtasPerSm = (3 * kBytes + kStatic <= kSmemPerCta2) ? 2 : 1;
+  static constexpr int kBudget = (kCtasPerSm == 2 ? kSmemPerCta2 : kSmemPerCta1) - kStatic;
+  static constexpr int kFit = kBudget / kBytes;
+  static constexpr int kStages = kFit > 5 ? 5 : kFit;
 };
 
 __device__ __forceinline__ int esize(int dtype) { return dtype == CARRY_F32 ? 4 : 2; }
@@ -254,14 +264,22 @@ __device__ __forceinline__ void act16_pairs(const uint8_t* base, int first, floa
 __device__ __noinline__ float exact_code(float t, float s) { return rintf(__fdiv_rn(t, s)); }
 
 // Re-decide one element whose remainder sits within the tie guard: the code is
-// rint of the true quotient.  `y` is code + kMagicRound, `e` the remainder.
-__device__ __forceinline__ void redecide(float& e, float& y, float s, float thr) {
+// rint of the true quotient target / s.  `y` is code + kMagicRound, `e` the remainder.
+__device__ __forceinline__ void redecide(float t, float& e, float& y, float s, float thr) {
   if (fabsf(e) > thr) {
-    const float code_old = __fadd_rn(y, -kMagicRound);
-    const float t = __fadd_rn(e, __fmul_rn(code_old, s));     // exact: the remainder was formed exactly
     const float code = exact_code(t, s);
     y = __fadd_rn(code, kMagicRound);
-    e = __fadd_rn(t, -__fmul_rn(code, s));
+    e = fmaf(code, -s, t);
+  }
+}
+
+// Same, when the target was not kept: it is rebuilt from the remainder and the old code.
+__device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float thr) {
+  if (fabsf(e) > thr) {
+    const float t = fmaf(__fadd_rn(y, -kMagicRound), s, e);
+    const float code = exact_code(t, s);
+    y = __fadd_rn(code, kMagicRound);
+    e = fmaf(code, -s, t);
   }
 }
 
@@ -278,27 +296,67 @@ __device__ __noinline__ void gates_of(const KParams& p, int n, int hv, float& al
   }
 }
 
-// Load tile `it` of this CTA into stage it % S (called by one thread).
-template <int LAYOUT, int RES, int RSCALE>
-__device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_t* full_bar, const int* slot_cache,
-                                        int it) {
-  using L = StageLayout<RES, LAYOUT>;
-  constexpr int S = L::kStages;
-  const int qes = esize(p.qkv_dtype);
-  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
-  const int tile = (int)blockIdx.x + it * (int)gridDim.x;
-  const int n = tile / p.HV, hv = tile - n * p.HV;
-  uint8_t* sb = smem + (size_t)(it % S) * L::kBytes;
-  long long slot = 1;
+// What a CTA needs to know about one of its tiles before the data arrives.
+struct TileMeta {
+  int n, hv, slot;
+  float alpha, beta;
+  float k_mul, q_mul;   // 1/|k| and scale/|q| (1 when the L2 norm is off or on the statequant path)
+  float kq;             // <k, q> after those factors
+};
+
+// Computed by a whole warp straight from global memory: slot id, gates, and the
+// norms of k and q (4 elements per lane, then warp sums).
+__device__ __noinline__ void tile_meta(const KParams& p, int tile, int lane, TileMeta* dst) {
+  TileMeta m;
+  m.n = tile / p.HV;
+  m.hv = tile - m.n * p.HV;
+  m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
+  gates_of(p, m.n, m.hv, m.alpha, m.beta);
+  long long q_off, k_off;
   if (p.packed) {
-    slot = (it < kTileCache) ? slot_cache[it] : p.slot_idx[(long long)n * p.stride_idx];
-    if (slot >= p.num_slots) {
-      if (p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
-      slot = 0;
+    const int h = m.hv / (p.HV / p.H);
+    q_off = (long long)m.n * p.stride_mixed_tok + (long long)h * kT;
+    k_off = q_off + (long long)p.H * kT;
+  } else {
+    q_off = k_off = ((long long)m.n * p.HV + m.hv) * kT;
+  }
+  float ks = 0.f, qs = 0.f, kq = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float kv = load_as_float(p.k, k_off + 4 * lane + i, p.qkv_dtype);
+    const float qv = load_as_float(p.q, q_off + 4 * lane + i, p.qkv_dtype);
+    ks = fmaf(kv, kv, ks);
+    qs = fmaf(qv, qv, qs);
+    kq = fmaf(kv, qv, kq);
+  }
+  ks = warp_sum32(ks); qs = warp_sum32(qs); kq = warp_sum32(kq);
+  m.k_mul = 1.0f; m.q_mul = 1.0f;
+  if (p.packed) {
+    if (p.l2norm) {
+      m.k_mul = __frcp_rn(sqrtf(ks + 1e-6f));
+      m.q_mul = __frcp_rn(sqrtf(qs + 1e-6f));
     }
+    m.q_mul *= p.qscale;
+  }
+  m.kq = kq * (m.k_mul * m.q_mul);
+  if (lane == 0) *dst = m;
+  __syncwarp();
+}
+
+// Load one tile into stage `stage` (called by one thread).
+template <int LAYOUT, int RES, int RSCALE, int QDT>
+__device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_t* full_bar, int stage, int n, int hv,
+                                        long long slot) {
+  using L = StageLayout<RES, LAYOUT, QDT>;
+  constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
+  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
+  uint8_t* sb = smem + (size_t)stage * L::kBytes;
+  if (p.packed && slot >= p.num_slots) {
+    if (p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
+    slot = 0;
   }
   *reinterpret_cast<volatile int*>(sb + L::kHeader) = (int)slot;
-  uint64_t* bar = &full_bar[it % S];
+  uint64_t* bar = &full_bar[stage];
   if (slot <= 0) { mbar_arrive(bar); return; }
   constexpr long long KV = kT * kT;
   const int8_t* codes;
@@ -324,24 +382,29 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
     k = reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes;
     v = reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes;
   }
-  const uint32_t vec = (uint32_t)kT * qes;
-  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * vec);
+  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes);
   bulk_load(sb + L::kCodes, codes, kT * kT, bar);
   bulk_load(sb + L::kResid, resid, L::kResidBytes, bar);
   bulk_load(sb + L::kSScale, sscale, 512, bar);
   bulk_load(sb + L::kRScale, rscale, rscale_bytes, bar);
-  bulk_load(sb + L::kQ, q, vec, bar);
-  bulk_load(sb + L::kK, k, vec, bar);
-  bulk_load(sb + L::kV, v, vec, bar);
+  bulk_load(sb + L::kQ, q, L::kVecBytes, bar);
+  bulk_load(sb + L::kK, k, L::kVecBytes, bar);
+  bulk_load(sb + L::kV, v, L::kVecBytes, bar);
 }
 
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
+struct StoreDesc {          // one bulk store of a warp's 16 rows (per lane 0..3: codes, residual, scales)
+  unsigned long long base;  // destination tensor
+  long long major, minor;   // bytes per slot (or per (request, head)) and per head
+  int row, src;             // bytes per warp share; offset of the source inside the stage
+};
+
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__global__ void __launch_bounds__(kThreads, (StageLayout<RES, LAYOUT>::kCtasPerSm))
+__global__ void __launch_bounds__(kThreads, (StageLayout<RES, LAYOUT, QDT>::kCtasPerSm))
 gdn_tile128_kernel(const __grid_constant__ KParams p) {
-  using L = StageLayout<RES, LAYOUT>;
+  using L = StageLayout<RES, LAYOUT, QDT>;
   constexpr int S = L::kStages;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full_bar[S];
@@ -349,9 +412,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   __shared__ int done_cnt[S];                        // warps whose stores of a stage have left shared memory
   __shared__ int poison_flag;
   __shared__ float head_red[2][kWarps];
-  __shared__ int slot_cache[kTileCache];             // slot ids of this CTA's first tiles
-  __shared__ float alpha_cache[kTileCache], beta_cache[kTileCache];
+  __shared__ TileMeta meta_cache[kTileCache + kWarps];   // this CTA's first tiles; one spare entry per warp
+  __shared__ StoreDesc store_tab[4];
+  __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? kWarps * kT : 4];   // per warp: q, scaled, as pairs
   __shared__ __align__(16) float col_red[(LAYOUT == LAYOUT_KV) ? kWarps * kT * 4 : 4];
+  static_assert(sizeof(full_bar) + sizeof(meet_bar) + sizeof(done_cnt) + sizeof(head_red) + sizeof(meta_cache) +
+                        sizeof(store_tab) + sizeof(q_warp) + sizeof(col_red) + 64 <= L::kStatic,
+                "static shared memory exceeds what the stage ring was sized for");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int total = p.B * p.HV;
@@ -364,21 +431,35 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     for (int s = 0; s < 3; ++s) mbar_init(&meet_bar[s], kWarps);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // slot ids and gates of this CTA's first tiles: one trip to global memory, up front
-  for (int i = tid; i < my_tiles && i < kTileCache; i += kThreads) {
-    const int tile = (int)blockIdx.x + i * (int)gridDim.x;
-    const int n = tile / p.HV, hv = tile - n * p.HV;
-    slot_cache[i] = p.packed ? p.slot_idx[(long long)n * p.stride_idx] : 1;
-    float a, b;
-    gates_of(p, n, hv, a, b);
-    alpha_cache[i] = a;
-    beta_cache[i] = b;
+  if (tid < 4) {
+    // lane t of every warp stores: 0 codes, 1 residual, 2 state scales, 3 residual scales (per V only)
+    StoreDesc d;
+    const long long head_b[4] = {kT * kT, L::kResidBytes, kT * 4, kT * 4};
+    const long long slot_b[4] = {p.stride_state_slot, p.stride_resid_slot, p.stride_sscale_slot * 4,
+                                 p.stride_rscale_slot * 4};
+    const void* base[4] = {p.codes_out, p.resid_out, p.sscale_out, p.rscale_out};
+    const int src[4] = {L::kCodes, L::kResid, L::kSScale, L::kRScale};
+    d.base = reinterpret_cast<unsigned long long>(base[tid]);
+    d.major = p.packed ? slot_b[tid] : head_b[tid];
+    d.minor = p.packed ? head_b[tid] : 0;
+    d.row = (int)(head_b[tid] / kWarps);
+    d.src = src[tid];
+    store_tab[tid] = d;
   }
+  // slot ids, gates and norms of this CTA's first tiles: one trip to global memory, up front
+  for (int i = warp; i < my_tiles && i < kTileCache; i += kWarps)
+    tile_meta(p, (int)blockIdx.x + i * (int)gridDim.x, lane, &meta_cache[i]);
   __syncthreads();
 
   if (tid == 0) {
     const int pre = my_tiles < S ? my_tiles : S;
-    for (int it = 0; it < pre; ++it) issue_tile<LAYOUT, RES, RSCALE>(p, smem, full_bar, slot_cache, it);
+    for (int it = 0; it < pre; ++it) {
+      int tn, thv, tslot;
+      if (it < kTileCache) { tn = meta_cache[it].n; thv = meta_cache[it].hv; tslot = meta_cache[it].slot; }
+      else { const int tile = (int)blockIdx.x + it * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
+             tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
+      issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, it % S, tn, thv, tslot);
+    }
   }
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
@@ -395,13 +476,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const int s = it % S;
     const uint32_t parity = (uint32_t)(it / S) & 1u;
     uint8_t* sb = smem + (size_t)s * L::kBytes;
-    const int tile = (int)blockIdx.x + it * (int)gridDim.x;
-    const int n = tile / p.HV, hv = tile - n * p.HV;
+    const TileMeta* tm = &meta_cache[it < kTileCache ? it : kTileCache + warp];
+    if (it >= kTileCache) tile_meta(p, (int)blockIdx.x + it * (int)gridDim.x, lane, &meta_cache[kTileCache + warp]);
+    const int n = tm->n, hv = tm->hv;
 
     mbar_wait(&full_bar[s], parity, poison, p.status);
-#ifdef CARRY_PROFILE
-    if (blockIdx.x == 0 && tid == 0 && p.prof && it < 64) p.prof[16 + it] = clock64() - prof_t;
-#endif
     PROF_MARK(0)
     const int slot = *reinterpret_cast<volatile int*>(sb + L::kHeader);
     const long long out_off = ((long long)n * p.HV + hv) * kT;
@@ -410,21 +489,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     if (!live) {
       if (slot <= 0 && tid < kT) store_from_float(p.out, out_off + tid, p.o_dtype, 0.f);
     } else {
-      float alpha, beta;
-      if (it < kTileCache) { alpha = alpha_cache[it]; beta = beta_cache[it]; }
-      else gates_of(p, n, hv, alpha, beta);
-
-      float k_mul = 1.0f, q_mul = 1.0f;
-      if (p.packed) {
-        if (p.l2norm) {                 // every warp on its own: 4 elements per lane, then a warp sum
-          const float4 k4 = act4<QDT>(sb + L::kK, 4 * lane), q4 = act4<QDT>(sb + L::kQ, 4 * lane);
-          const float ks = fmaf(k4.x, k4.x, fmaf(k4.y, k4.y, fmaf(k4.z, k4.z, k4.w * k4.w)));
-          const float qs = fmaf(q4.x, q4.x, fmaf(q4.y, q4.y, fmaf(q4.z, q4.z, q4.w * q4.w)));
-          k_mul = __frcp_rn(sqrtf(warp_sum32(ks) + 1e-6f));
-          q_mul = __frcp_rn(sqrtf(warp_sum32(qs) + 1e-6f));
-        }
-        q_mul *= p.qscale;
-      }
+      const float alpha = tm->alpha, beta = tm->beta, k_mul = tm->k_mul, q_mul = tm->q_mul, kq = tm->kq;
       const float* sscale = reinterpret_cast<const float*>(sb + L::kSScale);
       const float* rscale = reinterpret_cast<const float*>(sb + L::kRScale);
       const float es_head = (RSCALE == CARRY_SCALE_PER_HEAD) ? rscale[hv] : 0.f;
@@ -436,100 +501,103 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // word of codes) is held as two pairs: E = {col 0, col 2}, O = {col 1, col 3}.
         const int cg = lane & 7, rg = lane >> 3;
         const int r0 = 16 * warp + 4 * rg, c0 = 16 * cg;
-        float2 kE[4], kO[4], qE[4], qO[4];
-        act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
-        act16_pairs<QDT>(sb + L::kQ, c0, q_mul, qE, qO);
-        float kq;
-        {
-          float2 acc = make_float2(0.f, 0.f);
-#pragma unroll
-          for (int m = 0; m < 4; ++m) { acc = fma2(kE[m], qE[m], acc); acc = fma2(kO[m], qO[m], acc); }
-          kq = warp_sum8(acc.x + acc.y);
+        float* qw = q_warp + warp * kT;
+        {   // this warp's copy of q: fp32, scaled, each quad stored as {q0, q2, q1, q3}
+          const float4 q4 = act4<QDT>(sb + L::kQ, 4 * lane);
+          *reinterpret_cast<float4*>(qw + 4 * lane) = make_float4(q4.x * q_mul, q4.z * q_mul, q4.y * q_mul, q4.w * q_mul);
         }
+        float2 kE[4], kO[4];
+        act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
+        __syncwarp();
 
         float2 hE[4][4], hO[4][4];       // [row][quad]
-        float dk[4], dq[4], srow[4], vrow[4];
+        float dk[4], dq[4];
+        // phase 1: dequantise, decay, partial dot products along the row
         {
           const float4 s4 = *reinterpret_cast<const float4*>(sscale + r0);
-          srow[0] = s4.x; srow[1] = s4.y; srow[2] = s4.z; srow[3] = s4.w;
-          const float4 v4 = act4<QDT>(sb + L::kV, r0);
-          vrow[0] = v4.x; vrow[1] = v4.y; vrow[2] = v4.z; vrow[3] = v4.w;
-        }
-        // phase 1: dequantise, decay, partial dot products along the row
+          const float srow[4] = {s4.x, s4.y, s4.z, s4.w};
+          const uint32_t q_addr = smem_u32(qw + c0);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
-          const uint32_t w[4] = {cw.x ^ 0x80808080u, cw.y ^ 0x80808080u, cw.z ^ 0x80808080u, cw.w ^ 0x80808080u};
-          const float2 s2 = splat(srow[i]);
-          float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
+          for (int i = 0; i < 4; ++i) {
+            const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
+            const uint32_t w[4] = {cw.x ^ 0x80808080u, cw.y ^ 0x80808080u, cw.z ^ 0x80808080u, cw.w ^ 0x80808080u};
+            const float2 s2 = splat(srow[i]);
+            float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
 #pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float2 e = mul2(mul2(s8x2_to_float<0, 2>(w[m]), s2), alpha2);
-            const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
-            hE[i][m] = e; hO[i][m] = o;
-            ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
-            aq = fma2(e, qE[m], aq); aq = fma2(o, qO[m], aq);
+            for (int m = 0; m < 4; ++m) {
+              const float2 e = mul2(mul2(s8x2_to_float<0, 2>(w[m]), s2), alpha2);
+              const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
+              hE[i][m] = e; hO[i][m] = o;
+              float2 qe, qo;       // re-read per row on purpose: q must not stay in registers
+              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                           : "=f"(qe.x), "=f"(qe.y), "=f"(qo.x), "=f"(qo.y) : "r"(q_addr + 16 * m));
+              ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
+              aq = fma2(e, qe, aq); aq = fma2(o, qo, aq);
+            }
+            dk[i] = ak.x + ak.y; dq[i] = aq.x + aq.y;
           }
-          dk[i] = ak.x + ak.y; dq[i] = aq.x + aq.y;
         }
         PROF_MARK(1)
 #pragma unroll
         for (int i = 0; i < 4; ++i) { dk[i] = warp_sum8(dk[i]); dq[i] = warp_sum8(dq[i]); }
         PROF_MARK(2)
 
-        // phase 2: rank-1 write, add the residual, row maxima
-        float amax[4], oval[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float dv = __fmul_rn(beta, __fadd_rn(vrow[i], -dk[i]));
-          oval[i] = fmaf(dv, kq, dq[i]);
-          const float2 dv2 = splat(dv);
-          const float es = (RSCALE == CARRY_SCALE_PER_V) ? rscale[r0 + i] : es_head;
-          float am = 0.f;
-          if constexpr (RES == CARRY_RES_INT4) {
-            const uint2 rw = *reinterpret_cast<const uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2);
-            const uint32_t w[2] = {rw.x ^ 0x88888888u, rw.y ^ 0x88888888u};
-            const float2 es2 = splat(es), es16 = splat(es * 0.0625f);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              float2 lo, hi;
-              if (m & 1) s4x4_to_float<2, 3>(w[m >> 1], lo, hi); else s4x4_to_float<0, 1>(w[m >> 1], lo, hi);
-              const float2 te = add2(add2(hE[i][m], mul2(kE[m], dv2)), mul2(lo, es2));
-              const float2 to = add2(add2(hO[i][m], mul2(kO[m], dv2)), mul2(hi, es16));
-              hE[i][m] = te; hO[i][m] = to;
-              am = max3abs(max3abs(am, te), to);
-            }
-          } else {
-            const uint4 rw = *reinterpret_cast<const uint4*>(sb + L::kResid + (r0 + i) * kT + c0);
-            const uint32_t w[4] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u, rw.z ^ 0x80808080u, rw.w ^ 0x80808080u};
-            const float2 es2 = splat(es);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const float2 te = add2(add2(hE[i][m], mul2(kE[m], dv2)), mul2(s8x2_to_float<0, 2>(w[m]), es2));
-              const float2 to = add2(add2(hO[i][m], mul2(kO[m], dv2)), mul2(s8x2_to_float<1, 3>(w[m]), es2));
-              hE[i][m] = te; hO[i][m] = to;
-              am = max3abs(max3abs(am, te), to);
+        // phase 2: rank-1 write and residual, each one fused multiply-add; row maxima
+        float amax[4], dvr[4];
+        {
+          const float4 v4 = act4<QDT>(sb + L::kV, r0);
+          dvr[0] = __fmul_rn(beta, __fadd_rn(v4.x, -dk[0])); dvr[1] = __fmul_rn(beta, __fadd_rn(v4.y, -dk[1]));
+          dvr[2] = __fmul_rn(beta, __fadd_rn(v4.z, -dk[2])); dvr[3] = __fmul_rn(beta, __fadd_rn(v4.w, -dk[3]));
+          if (cg == 0) {                      // four consecutive outputs of this lane's rows
+            const float o0 = fmaf(dvr[0], kq, dq[0]), o1 = fmaf(dvr[1], kq, dq[1]);
+            const float o2 = fmaf(dvr[2], kq, dq[2]), o3 = fmaf(dvr[3], kq, dq[3]);
+            if (p.o_dtype == CARRY_F32) {
+              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_off + r0) = make_float4(o0, o1, o2, o3);
+            } else if (p.o_dtype == CARRY_BF16) {
+              const __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
+              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off + r0) =
+                  make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+            } else {
+              const __half2 a = __floats2half2_rn(o0, o1), b = __floats2half2_rn(o2, o3);
+              *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + out_off + r0) =
+                  make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
             }
           }
-          amax[i] = am;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 dv2 = splat(dvr[i]);
+            const float es = (RSCALE == CARRY_SCALE_PER_V) ? rscale[r0 + i] : es_head;
+            float am = 0.f;
+            if constexpr (RES == CARRY_RES_INT4) {
+              const uint2 rw = *reinterpret_cast<const uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2);
+              const uint32_t w[2] = {rw.x ^ 0x88888888u, rw.y ^ 0x88888888u};
+              const float2 es2 = splat(es), es16 = splat(es * 0.0625f);
+#pragma unroll
+              for (int m = 0; m < 4; ++m) {
+                float2 lo, hi;
+                if (m & 1) s4x4_to_float<2, 3>(w[m >> 1], lo, hi); else s4x4_to_float<0, 1>(w[m >> 1], lo, hi);
+                const float2 te = fma2(lo, es2, fma2(kE[m], dv2, hE[i][m]));
+                const float2 to = fma2(hi, es16, fma2(kO[m], dv2, hO[i][m]));
+                hE[i][m] = te; hO[i][m] = to;
+                am = max3abs(max3abs(am, te), to);
+              }
+            } else {
+              const uint4 rw = *reinterpret_cast<const uint4*>(sb + L::kResid + (r0 + i) * kT + c0);
+              const uint32_t w[4] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u, rw.z ^ 0x80808080u, rw.w ^ 0x80808080u};
+              const float2 es2 = splat(es);
+#pragma unroll
+              for (int m = 0; m < 4; ++m) {
+                const float2 te = fma2(s8x2_to_float<0, 2>(w[m]), es2, fma2(kE[m], dv2, hE[i][m]));
+                const float2 to = fma2(s8x2_to_float<1, 3>(w[m]), es2, fma2(kO[m], dv2, hO[i][m]));
+                hE[i][m] = te; hO[i][m] = to;
+                am = max3abs(max3abs(am, te), to);
+              }
+            }
+            amax[i] = am;
+          }
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) amax[i] = warp_max8(amax[i]);
-        if (cg == 0) {                      // four consecutive outputs of this lane's rows
-          if (p.o_dtype == CARRY_F32) {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_off + r0) =
-                make_float4(oval[0], oval[1], oval[2], oval[3]);
-          } else if (p.o_dtype == CARRY_BF16) {
-            const __nv_bfloat162 a = __floats2bfloat162_rn(oval[0], oval[1]), b = __floats2bfloat162_rn(oval[2], oval[3]);
-            *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off + r0) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-          } else {
-            const __half2 a = __floats2half2_rn(oval[0], oval[1]), b = __floats2half2_rn(oval[2], oval[3]);
-            *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + out_off + r0) =
-                make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-          }
-        }
-
         // new state scales: lane cg of a row group does row cg's divisions, then they are shared
         float snew[4], sinv[4];
         {
@@ -541,45 +609,57 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
             sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
           }
+          if (cg == 0)
+            *reinterpret_cast<float4*>(sb + L::kSScale + r0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
         }
-
         PROF_MARK(3)
-        // phase 3: state codes, new residual
+
+        // phase 3: state codes, new residual (target - code * scale as one fused multiply-add)
         float eamax[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 inv2 = splat(sinv[i]), ns2 = splat(-snew[i]);
-          float2 yE[4], yO[4];
-          float em = 0.f;
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            yE[m] = add2(mul2(hE[i][m], inv2), magic2);
-            yO[m] = add2(mul2(hO[i][m], inv2), magic2);
-            hE[i][m] = add2(hE[i][m], mul2(add2(yE[m], nmagic2), ns2));
-            hO[i][m] = add2(hO[i][m], mul2(add2(yO[m], nmagic2), ns2));
-            em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
-          }
           const float thr = snew[i] * kTieGuard;
-          if (em > thr) {                    // rare: a quotient within the tie guard somewhere in these 16
-            em = 0.f;
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              redecide(hE[i][m].x, yE[m].x, snew[i], thr); redecide(hE[i][m].y, yE[m].y, snew[i], thr);
-              redecide(hO[i][m].x, yO[m].x, snew[i], thr); redecide(hO[i][m].y, yO[m].y, snew[i], thr);
-              em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
-            }
-          }
+          float em = 0.f;
           uint32_t packed[4];
 #pragma unroll
-          for (int m = 0; m < 4; ++m)
-            packed[m] = pack4(__float_as_uint(yE[m].x), __float_as_uint(yO[m].x), __float_as_uint(yE[m].y),
-                              __float_as_uint(yO[m].y));
+          for (int hf = 0; hf < 2; ++hf) {           // 8 elements at a time keeps the temporaries small
+            float2 yE[2], yO[2], eE[2], eO[2];
+            float em8 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int m = 2 * hf + j;
+              yE[j] = fma2(hE[i][m], inv2, magic2);
+              yO[j] = fma2(hO[i][m], inv2, magic2);
+              eE[j] = fma2(add2(yE[j], nmagic2), ns2, hE[i][m]);
+              eO[j] = fma2(add2(yO[j], nmagic2), ns2, hO[i][m]);
+              em8 = max3abs(max3abs(em8, eE[j]), eO[j]);
+            }
+            if (em8 > thr) {                   // rare: a quotient within the tie guard somewhere in these 8
+              em8 = 0.f;
+#pragma unroll
+              for (int j = 0; j < 2; ++j) {
+                const int m = 2 * hf + j;
+                redecide(hE[i][m].x, eE[j].x, yE[j].x, snew[i], thr); redecide(hE[i][m].y, eE[j].y, yE[j].y, snew[i], thr);
+                redecide(hO[i][m].x, eO[j].x, yO[j].x, snew[i], thr); redecide(hO[i][m].y, eO[j].y, yO[j].y, snew[i], thr);
+                em8 = max3abs(max3abs(em8, eE[j]), eO[j]);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int m = 2 * hf + j;
+              packed[m] = pack4(__float_as_uint(yE[j].x), __float_as_uint(yO[j].x), __float_as_uint(yE[j].y),
+                                __float_as_uint(yO[j].y));
+              hE[i][m] = eE[j]; hO[i][m] = eO[j];
+            }
+            em = fmaxf(em, em8);
+          }
           *reinterpret_cast<uint4*>(sb + L::kCodes + (r0 + i) * kT + c0) =
               make_uint4(packed[0], packed[1], packed[2], packed[3]);
           eamax[i] = em;
         }
-
         PROF_MARK(4)
+
         // phase 4: residual scale and codes
         float esn[4], einv[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
@@ -617,8 +697,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             uint32_t by[8];
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
-              const float2 ye = add2(mul2(hE[i][m], invE), mE);
-              const float2 co = add2(add2(mul2(hO[i][m], invE), magic2), nmagic2);
+              const float2 ye = fma2(hE[i][m], invE, mE);
+              const float2 co = add2(fma2(hO[i][m], invE, magic2), nmagic2);
               const float2 pk = fma2(co, sixteen, ye);
               by[2 * m] = __float_as_uint(pk.x);
               by[2 * m + 1] = __float_as_uint(pk.y);
@@ -630,8 +710,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             uint32_t packed[4];
 #pragma unroll
             for (int m = 0; m < 4; ++m) {
-              const float2 ye = add2(mul2(hE[i][m], invE), magic2);
-              const float2 yo = add2(mul2(hO[i][m], invE), magic2);
+              const float2 ye = fma2(hE[i][m], invE, magic2);
+              const float2 yo = fma2(hO[i][m], invE, magic2);
               packed[m] = pack4(__float_as_uint(ye.x), __float_as_uint(yo.x), __float_as_uint(ye.y),
                                 __float_as_uint(yo.y));
             }
@@ -639,11 +719,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
                 make_uint4(packed[0], packed[1], packed[2], packed[3]);
           }
         }
-        if (cg == 0) {
-          *reinterpret_cast<float4*>(sb + L::kSScale + r0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
-          if (RSCALE == CARRY_SCALE_PER_V)
-            *reinterpret_cast<float4*>(sb + L::kRScale + r0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
-        }
+        if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
+          *reinterpret_cast<float4*>(sb + L::kRScale + r0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
         if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) {
           float* dst = p.packed ? p.rscale_out + (long long)slot * p.stride_rscale_slot + hv
                                 : p.rscale_out + (long long)n * p.HV + hv;
@@ -656,11 +733,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         float* red_dot = col_red;                       // [warp][col][2]
         float* red_max = col_red + kWarps * kT * 2;     // [warp][col]
         float* red_emax = red_max + kWarps * kT;        // [warp][col]
-        float kq;
-        {
-          const float4 k4 = act4<QDT>(sb + L::kK, 4 * lane), q4 = act4<QDT>(sb + L::kQ, 4 * lane);
-          kq = warp_sum32(fmaf(k4.x, q4.x, fmaf(k4.y, q4.y, fmaf(k4.z, q4.z, k4.w * q4.w)))) * (k_mul * q_mul);
-        }
         float krow[16], qrow[16];            // k and q of this warp's 16 rows (the same in every lane)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -728,8 +800,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             eB = mul2(s8x2_to_float<2, 3>(w), make_float2(es_col[2], es_col[3]));
           }
           const float2 kr = splat(krow[i]);
-          const float2 tA = add2(add2(hA[i], mul2(kr, dvA)), eA);
-          const float2 tB = add2(add2(hB[i], mul2(kr, dvB)), eB);
+          const float2 tA = add2(fma2(kr, dvA, hA[i]), eA);
+          const float2 tB = add2(fma2(kr, dvB, hB[i]), eB);
           hA[i] = tA; hB[i] = tB;
           amax[0] = fmaxf(amax[0], fabsf(tA.x)); amax[1] = fmaxf(amax[1], fabsf(tA.y));
           amax[2] = fmaxf(amax[2], fabsf(tB.x)); amax[3] = fmaxf(amax[3], fabsf(tB.y));
@@ -756,9 +828,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         uint32_t cw[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 yA = add2(mul2(hA[i], invA), magic2), yB = add2(mul2(hB[i], invB), magic2);
-          hA[i] = add2(hA[i], mul2(add2(yA, nmagic2), nsA));
-          hB[i] = add2(hB[i], mul2(add2(yB, nmagic2), nsB));
+          const float2 yA = fma2(hA[i], invA, magic2), yB = fma2(hB[i], invB, magic2);
+          hA[i] = fma2(add2(yA, nmagic2), nsA, hA[i]);
+          hB[i] = fma2(add2(yB, nmagic2), nsB, hB[i]);
           cw[i] = pack4(__float_as_uint(yA.x), __float_as_uint(yA.y), __float_as_uint(yB.x), __float_as_uint(yB.y));
           eamax[0] = fmaxf(eamax[0], fabsf(hA[i].x)); eamax[1] = fmaxf(eamax[1], fabsf(hA[i].y));
           eamax[2] = fmaxf(eamax[2], fabsf(hB[i].x)); eamax[3] = fmaxf(eamax[3], fabsf(hB[i].y));
@@ -769,8 +841,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           for (int i = 0; i < 16; ++i) {
             float2 yA = add2(s8x2_to_float<0, 1>(cw[i] ^ 0x80808080u), magic2);
             float2 yB = add2(s8x2_to_float<2, 3>(cw[i] ^ 0x80808080u), magic2);
-            redecide(hA[i].x, yA.x, snew[0], thr[0]); redecide(hA[i].y, yA.y, snew[1], thr[1]);
-            redecide(hB[i].x, yB.x, snew[2], thr[2]); redecide(hB[i].y, yB.y, snew[3], thr[3]);
+            redecide_rec(hA[i].x, yA.x, snew[0], thr[0]); redecide_rec(hA[i].y, yA.y, snew[1], thr[1]);
+            redecide_rec(hB[i].x, yB.x, snew[2], thr[2]); redecide_rec(hB[i].y, yB.y, snew[3], thr[3]);
             cw[i] = pack4(__float_as_uint(yA.x), __float_as_uint(yA.y), __float_as_uint(yB.x), __float_as_uint(yB.y));
             eamax[0] = fmaxf(eamax[0], fabsf(hA[i].x)); eamax[1] = fmaxf(eamax[1], fabsf(hA[i].y));
             eamax[2] = fmaxf(eamax[2], fabsf(hB[i].x)); eamax[3] = fmaxf(eamax[3], fabsf(hB[i].y));
@@ -804,7 +876,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         const float2 ieB = make_float2(__frcp_rn(esn[2]), __frcp_rn(esn[3]));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float2 rA = add2(mul2(hA[i], ieA), magic2), rB = add2(mul2(hB[i], ieB), magic2);
+          const float2 rA = fma2(hA[i], ieA, magic2), rB = fma2(hB[i], ieB, magic2);
           const uint32_t y0 = __float_as_uint(rA.x), y1 = __float_as_uint(rA.y);
           const uint32_t y2 = __float_as_uint(rB.x), y3 = __float_as_uint(rB.y);
           if constexpr (RES == CARRY_RES_INT4) {
@@ -827,69 +899,61 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     if (live) meet_parity ^= 1u;
     PROF_MARK(6)
 
-    // ---- this warp's 16 rows go back; free the previous stage; refill it ---------
+    // ---- this warp's 16 rows go back: lanes 0..3 each issue one bulk store ------------
     __syncwarp();
     fence_async_smem();
     __syncwarp();
     PROF_MARK(7)
-    if (lane == 0) {
+    constexpr int kStorers = (RSCALE == CARRY_SCALE_PER_V) ? 4 : 3;
+    const bool recycle = it > 0 && it - 1 + S < my_tiles;
+    if (lane < kStorers) {
       if (live && !*poison) {
-        int8_t* codes_out;
-        uint8_t* resid_out;
-        float *ss_out, *rs_out;
-        if (p.packed) {
-          codes_out = p.codes_out + (long long)slot * p.stride_state_slot + (long long)hv * kT * kT;
-          resid_out = reinterpret_cast<uint8_t*>(p.resid_out) + (long long)slot * p.stride_resid_slot +
-                      (long long)hv * L::kResidBytes;
-          ss_out = p.sscale_out + (long long)slot * p.stride_sscale_slot + (long long)hv * kT;
-          rs_out = p.rscale_out + (long long)slot * p.stride_rscale_slot + (long long)hv * kT;
-        } else {
-          const long long nh = (long long)n * p.HV + hv;
-          codes_out = p.codes_out + nh * kT * kT;
-          resid_out = reinterpret_cast<uint8_t*>(p.resid_out) + nh * L::kResidBytes;
-          ss_out = p.sscale_out + nh * kT;
-          rs_out = p.rscale_out + nh * kT;
-        }
-        constexpr int kRowsB = 16 * kT;                       // bytes of 16 rows of codes
-        constexpr int kResRowsB = L::kResidBytes / kWarps;    // bytes of 16 rows of residual
-        bulk_store(codes_out + warp * kRowsB, sb + L::kCodes + warp * kRowsB, kRowsB);
-        bulk_store(resid_out + warp * kResRowsB, sb + L::kResid + warp * kResRowsB, kResRowsB);
-        bulk_store(ss_out + warp * 16, sb + L::kSScale + warp * 64, 64);
-        if (RSCALE == CARRY_SCALE_PER_V) bulk_store(rs_out + warp * 16, sb + L::kRScale + warp * 64, 64);
+        const StoreDesc d = store_tab[lane];
+        const long long major = p.packed ? (long long)slot : (long long)n * p.HV + hv;
+        const long long minor = p.packed ? (long long)hv : 0;
+        bulk_store(reinterpret_cast<void*>(d.base + major * d.major + minor * d.minor + (long long)warp * d.row),
+                   sb + d.src + warp * d.row, (uint32_t)d.row);
       }
       bulk_commit();
-      PROF_MARK(8)
-      // Stage (it-1) % S is free once every warp's stores of tile it-1 have left
-      // shared memory.  The warp that observes this last refills the stage, so
-      // nobody waits here.
-      if (it > 0 && it - 1 + S < my_tiles) {
-        bulk_wait_read<1>();
-        PROF_MARK(9)
+      if (recycle) bulk_wait_read<1>();     // the previous tile's stores have left shared memory
+    }
+    PROF_MARK(8)
+    // Stage (it-1) % S is free once every warp's stores of tile it-1 have left
+    // shared memory.  The warp that observes this last refills the stage, so
+    // nobody waits here.
+    if (recycle) {
+      __syncwarp();
+      if (lane == 0) {
         __threadfence_block();
         const int prev = (it - 1) % S;
         if (atomicAdd(&done_cnt[prev], 1) == kWarps - 1) {
           __threadfence_block();
           done_cnt[prev] = 0;
-          if (!*poison) issue_tile<LAYOUT, RES, RSCALE>(p, smem, full_bar, slot_cache, it - 1 + S);
+          if (!*poison) {
+            const int nit = it - 1 + S;
+            int tn, thv, tslot;
+            if (nit < kTileCache) { tn = meta_cache[nit].n; thv = meta_cache[nit].hv; tslot = meta_cache[nit].slot; }
+            else { const int tile = (int)blockIdx.x + nit * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
+                   tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
+            issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, prev, tn, thv, tslot);
+          }
         }
       }
     }
     PROF_MARK(10)
-    __syncwarp();
-    PROF_MARK(11)
   }
 #ifdef CARRY_PROFILE
   if (lane == 0 && p.prof) {
     for (int k = 0; k < 12; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.prof) + k, (unsigned long long)prof_acc[k]);
   }
 #endif
-  if (lane == 0) bulk_wait_read<0>();
+  if (lane < 4) bulk_wait_read<0>();
   __syncthreads();
 }
 
 template <int LAYOUT, int RES, int RSCALE, int QDT>
 int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
-  using L = StageLayout<RES, LAYOUT>;
+  using L = StageLayout<RES, LAYOUT, QDT>;
   auto kern = gdn_tile128_kernel<LAYOUT, RES, RSCALE, QDT>;
   const size_t smem = (size_t)L::kBytes * L::kStages;
   static thread_local bool configured[64] = {false};
