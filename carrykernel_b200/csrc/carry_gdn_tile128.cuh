@@ -3,12 +3,14 @@
 // residual; all of it is contiguous in memory in both layouts, so every tile
 // moves with a handful of 1-D bulk async copies (TMA, no tensor map):
 //
-//   global --cp.async.bulk--> shared stage --(registers)--> same shared stage
-//          --cp.async.bulk--> global
+//   global --cp.async.bulk--> shared stage --> registers --16-byte stores--> global
 //
 // Persistent CTAs (two per SM) walk the tile list with a ring of stages: while
-// one tile is computed, the loads of the next ones are in flight and the stores
-// of the previous one drain.  The state is read from HBM once and written once.
+// one tile is computed, the loads of the next ones are in flight.  A stage is
+// handed back as soon as its last byte has been read (before the tile is
+// quantised), and results leave straight from registers as 16-byte vector
+// stores that cover whole 128-byte lines.  The state is read from HBM once and
+// written once.
 //
 // Work split inside a CTA (256 threads = 8 warps): warp w owns memory rows
 // 16w..16w+15 of the tile.
@@ -20,13 +22,12 @@
 //   * statequant layout [K][V] (scale per column): lane = 4 contiguous columns
 //     x the warp's 16 rows; column sums are finished across the 8 warps through
 //     shared memory.
-// Each warp stores its own 16 rows back, so no CTA-wide barrier guards stores.
 //
 // Arithmetic keeps the reference's operation order for everything that feeds a
 // state code: (code*scale)*alpha, h + (k*dv) with the product rounded first,
 // target - (code*scale) with the product rounded first.  round(target / s) is
 // evaluated as rint(target * (1/s)); the two can only differ when the quotient
-// is within ~3e-5 of a tie, which shows up as a remainder within 2^-14 of half
+// is within ~8e-6 of a tie, which shows up as a remainder within 2^-16 of half
 // a step -- groups of elements where that happens are re-decided with the true
 // division.  Residual codes use rint(e * (1/es)) as is.  Math runs as packed
 // f32x2 (IEEE round-to-nearest per component).
@@ -79,17 +80,6 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                : "memory");
 }
-__device__ __forceinline__ void bulk_store(void* dst_gmem, const void* src_smem, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst_gmem),
-               "r"(smem_u32(src_smem)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Bounded wait: after kSpinLimit failed polls the CTA is marked poisoned, the
 // status word gets the timeout bit and every later wait returns at once; a
@@ -103,20 +93,42 @@ __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
   *poison = 1;
   if (status) atomicOr(status, CARRY_GDN_STATUS_TIMEOUT);
 }
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* poison, int* status) {
-  if (*poison) return;
-  if (mbar_try_wait(bar, parity)) return;
-  mbar_wait_slow(bar, parity, poison, status);
+// returns false when the CTA is poisoned (the data behind the barrier must not be used)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* poison, int* status) {
+  if (mbar_try_wait(bar, parity)) return true;
+  if (!*poison) mbar_wait_slow(bar, parity, poison, status);
+  return !*poison;
+}
+__device__ __forceinline__ int lds_i32(const void* p) {
+  int v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 lds_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(smem_u32(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void stg_v4(unsigned long long addr, uint4 v) {
+  asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void stg_v2(unsigned long long addr, uint2 v) {
+  asm volatile("st.global.v2.b32 [%0], {%1, %2};" ::"l"(addr), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void stg_b32(unsigned long long addr, uint32_t v) {
+  asm volatile("st.global.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void stg_b16(unsigned long long addr, uint32_t v) {
+  asm volatile("st.global.b16 [%0], %1;" ::"l"(addr), "h"((unsigned short)v) : "memory");
 }
 
-// All 8 warps meet here: one arrival per warp, then a bounded wait (never a
-// bar.sync inside the tile loop, so nothing in it can wait without a limit).
-__device__ __forceinline__ void warps_meet(uint64_t* bar, uint32_t parity, int lane, volatile int* poison,
-                                           int* status) {
-  __syncwarp();
-  if (lane == 0) mbar_arrive(bar);
-  mbar_wait(bar, parity, poison, status);
-}
+// All 8 warps meet on a hardware named barrier.  Every thread of the CTA runs
+// the same number of tile iterations and reaches the same number of meetings in
+// each of them whether or not the tile is live (skipped tiles take them in the
+// else branch), so a meeting cannot be left waiting for a warp that never comes.
+// Waits on data in flight (the stage barriers) are the bounded ones.
+__device__ __forceinline__ void warps_meet(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kThreads) : "memory"); }
 
 // ---------------------------------------------------------------------------
 // packed fp32 helpers (each maps to one f32x2 instruction)
@@ -130,7 +142,7 @@ __device__ __forceinline__ float max3abs(float m, float2 x) { return fmaxf(fmaxf
 constexpr float kMagicRound = 12582912.0f;      // 1.5 * 2^23: x + M rounds x to an integer (RNE)
 constexpr float kMagicByte = 8388736.0f;        // 2^23 + 128
 constexpr float kMagicNib = 8388616.0f;         // 2^23 + 8
-constexpr float kTieGuard = 0.49993896484375f;  // 0.5 - 2^-14
+constexpr float kTieGuard = 0.4999847412109375f;  // 0.5 - 2^-16
 
 // bytes A and B of w (each already XOR-ed with 0x80) -> {float(code A), float(code B)}
 template <int A, int B>
@@ -196,11 +208,15 @@ struct StageLayout {
   static constexpr int kQ = kRScale + 512;                   // raw q, k, v of this head
   static constexpr int kK = kQ + kVecBytes;
   static constexpr int kV = kK + kVecBytes;
-  static constexpr int kHeader = kV + kVecBytes;             // int slot
-  static constexpr int kBytes = kHeader + 16;
+  static constexpr int kHeader = kV + kVecBytes;             // int slot, then the 4 destination pointers
+  static constexpr int kBytes = kHeader + 48;
   static constexpr int kStatic = (LAYOUT == 0) ? kStaticVK : kStaticKV;
   // two CTAs per SM when at least 3 stages fit next to the static part, else one
+#ifdef CARRY_FORCE_1CTA
+  static constexpr int kCtasPerSm = 1;
+#else
   static constexpr int kCtasPerSm = (3 * kBytes + kStatic <= kSmemPerCta2) ? 2 : 1;
+#endif
   static constexpr int kBudget = (kCtasPerSm == 2 ? kSmemPerCta2 : kSmemPerCta1) - kStatic;
   static constexpr int kFit = kBudget / kBytes;
   static constexpr int kStages = kFit > 5 ? 5 : kFit;
@@ -263,17 +279,9 @@ __device__ __forceinline__ void act16_pairs(const uint8_t* base, int first, floa
 
 __device__ __noinline__ float exact_code(float t, float s) { return rintf(__fdiv_rn(t, s)); }
 
-// Re-decide one element whose remainder sits within the tie guard: the code is
-// rint of the true quotient target / s.  `y` is code + kMagicRound, `e` the remainder.
-__device__ __forceinline__ void redecide(float t, float& e, float& y, float s, float thr) {
-  if (fabsf(e) > thr) {
-    const float code = exact_code(t, s);
-    y = __fadd_rn(code, kMagicRound);
-    e = fmaf(code, -s, t);
-  }
-}
-
-// Same, when the target was not kept: it is rebuilt from the remainder and the old code.
+// Re-decide one element whose remainder sits within the tie guard: its code becomes rint of the
+// true quotient target / s.  `y` is code + kMagicRound, `e` the remainder; the target is rebuilt
+// exactly from them (remainder and code * s add up to a representable number).
 __device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float thr) {
   if (fabsf(e) > thr) {
     const float t = fmaf(__fadd_rn(y, -kMagicRound), s, e);
@@ -358,6 +366,7 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
   *reinterpret_cast<volatile int*>(sb + L::kHeader) = (int)slot;
   uint64_t* bar = &full_bar[stage];
   if (slot <= 0) { mbar_arrive(bar); return; }
+  unsigned long long* dst = reinterpret_cast<unsigned long long*>(sb + L::kHeader + 16);
   constexpr long long KV = kT * kT;
   const int8_t* codes;
   const uint8_t *resid, *q, *k, *v;
@@ -372,6 +381,12 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
     q = row + (long long)h * kT * qes;
     k = row + ((long long)p.H * kT + (long long)h * kT) * qes;
     v = row + (2LL * p.H * kT + (long long)hv * kT) * qes;
+    // in place: the results go back where the tile came from
+    dst[0] = reinterpret_cast<unsigned long long>(codes);
+    dst[1] = reinterpret_cast<unsigned long long>(resid);
+    dst[2] = reinterpret_cast<unsigned long long>(sscale);
+    dst[3] = reinterpret_cast<unsigned long long>(p.rscale_out + slot * p.stride_rscale_slot +
+                                                  (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : (long long)hv));
   } else {
     const long long nh = (long long)n * p.HV + hv;
     codes = p.codes_in + nh * KV;
@@ -381,6 +396,10 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
     q = reinterpret_cast<const uint8_t*>(p.q) + nh * kT * qes;
     k = reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes;
     v = reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes;
+    dst[0] = reinterpret_cast<unsigned long long>(p.codes_out + nh * KV);
+    dst[1] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(p.resid_out) + nh * L::kResidBytes);
+    dst[2] = reinterpret_cast<unsigned long long>(p.sscale_out + nh * kT);
+    dst[3] = reinterpret_cast<unsigned long long>(p.rscale_out + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : nh));
   }
   mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes);
   bulk_load(sb + L::kCodes, codes, kT * kT, bar);
@@ -395,12 +414,6 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
 // ---------------------------------------------------------------------------
 // the kernel
 // ---------------------------------------------------------------------------
-struct StoreDesc {          // one bulk store of a warp's 16 rows (per lane 0..3: codes, residual, scales)
-  unsigned long long base;  // destination tensor
-  long long major, minor;   // bytes per slot (or per (request, head)) and per head
-  int row, src;             // bytes per warp share; offset of the source inside the stage
-};
-
 template <int LAYOUT, int RES, int RSCALE, int QDT>
 __global__ void __launch_bounds__(kThreads, (StageLayout<RES, LAYOUT, QDT>::kCtasPerSm))
 gdn_tile128_kernel(const __grid_constant__ KParams p) {
@@ -408,16 +421,15 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   constexpr int S = L::kStages;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full_bar[S];
-  __shared__ __align__(8) uint64_t meet_bar[3];
-  __shared__ int done_cnt[S];                        // warps whose stores of a stage have left shared memory
+  __shared__ int done_cnt[S];                        // warps that have finished reading a stage
+  __shared__ int first_cnt[2];                       // arrivals at the last meeting of a tile, by tile parity
   __shared__ int poison_flag;
   __shared__ float head_red[2][kWarps];
   __shared__ TileMeta meta_cache[kTileCache + kWarps];   // this CTA's first tiles; one spare entry per warp
-  __shared__ StoreDesc store_tab[4];
   __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? kWarps * kT : 4];   // per warp: q, scaled, as pairs
   __shared__ __align__(16) float col_red[(LAYOUT == LAYOUT_KV) ? kWarps * kT * 4 : 4];
-  static_assert(sizeof(full_bar) + sizeof(meet_bar) + sizeof(done_cnt) + sizeof(head_red) + sizeof(meta_cache) +
-                        sizeof(store_tab) + sizeof(q_warp) + sizeof(col_red) + 64 <= L::kStatic,
+  static_assert(sizeof(full_bar) + sizeof(done_cnt) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) +
+                        sizeof(q_warp) + sizeof(col_red) + 64 <= L::kStatic,
                 "static shared memory exceeds what the stage ring was sized for");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -428,23 +440,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   if (tid == 0) {
     poison_flag = 0;
     for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
-    for (int s = 0; s < 3; ++s) mbar_init(&meet_bar[s], kWarps);
+    first_cnt[0] = first_cnt[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (tid < 4) {
-    // lane t of every warp stores: 0 codes, 1 residual, 2 state scales, 3 residual scales (per V only)
-    StoreDesc d;
-    const long long head_b[4] = {kT * kT, L::kResidBytes, kT * 4, kT * 4};
-    const long long slot_b[4] = {p.stride_state_slot, p.stride_resid_slot, p.stride_sscale_slot * 4,
-                                 p.stride_rscale_slot * 4};
-    const void* base[4] = {p.codes_out, p.resid_out, p.sscale_out, p.rscale_out};
-    const int src[4] = {L::kCodes, L::kResid, L::kSScale, L::kRScale};
-    d.base = reinterpret_cast<unsigned long long>(base[tid]);
-    d.major = p.packed ? slot_b[tid] : head_b[tid];
-    d.minor = p.packed ? head_b[tid] : 0;
-    d.row = (int)(head_b[tid] / kWarps);
-    d.src = src[tid];
-    store_tab[tid] = d;
   }
   // slot ids, gates and norms of this CTA's first tiles: one trip to global memory, up front
   for (int i = warp; i < my_tiles && i < kTileCache; i += kWarps)
@@ -463,7 +460,24 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   }
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
-  uint32_t meet_parity = 0;            // flips once per computed tile
+  // Variants whose warps meet once per tile refill a stage one tile late: when tile `it` reaches its
+  // last meeting every warp has long left tile it-1, and the first warp to arrive -- the one with the
+  // most slack -- loads tile it-1+S into that stage while it waits for the others.  Variants without a
+  // meeting refill a stage as soon as its last reader is done with it.
+  constexpr bool kMeetRefill = (LAYOUT == LAYOUT_KV) || (RSCALE == CARRY_SCALE_PER_HEAD);
+  auto load_tile = [&](int nit) {
+    int tn, thv, tslot;
+    if (nit < kTileCache) { tn = meta_cache[nit].n; thv = meta_cache[nit].hv; tslot = meta_cache[nit].slot; }
+    else { const int tile = (int)blockIdx.x + nit * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
+           tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, nit % S, tn, thv, tslot);
+  };
+  auto refill_at_meeting = [&](int it) {          // called by lane 0 of every warp right before the last meeting
+    if (atomicAdd(&first_cnt[it & 1], 1) == 0) {
+      first_cnt[(it + 1) & 1] = 0;
+      if (it > 0 && it - 1 + S < my_tiles && !*poison) load_tile(it - 1 + S);
+    }
+  };
 
 #ifdef CARRY_PROFILE
   long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
@@ -480,14 +494,22 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     if (it >= kTileCache) tile_meta(p, (int)blockIdx.x + it * (int)gridDim.x, lane, &meta_cache[kTileCache + warp]);
     const int n = tm->n, hv = tm->hv;
 
-    mbar_wait(&full_bar[s], parity, poison, p.status);
+    const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
     PROF_MARK(0)
-    const int slot = *reinterpret_cast<volatile int*>(sb + L::kHeader);
+    const int slot = lds_i32(sb + L::kHeader);
     const long long out_off = ((long long)n * p.HV + hv) * kT;
-    const bool live = slot > 0 && !*poison;
+    const bool live = slot > 0 && healthy;
+    unsigned long long dst_codes = 0, dst_resid = 0, dst_sscale = 0, dst_rscale = 0;
+    if (live) {
+      const uint4 d0 = lds_v4(sb + L::kHeader + 16), d1 = lds_v4(sb + L::kHeader + 32);
+      dst_codes = ((unsigned long long)d0.y << 32) | d0.x; dst_resid = ((unsigned long long)d0.w << 32) | d0.z;
+      dst_sscale = ((unsigned long long)d1.y << 32) | d1.x; dst_rscale = ((unsigned long long)d1.w << 32) | d1.z;
+    }
 
     if (!live) {
       if (slot <= 0 && tid < kT) store_from_float(p.out, out_off + tid, p.o_dtype, 0.f);
+      if (LAYOUT == LAYOUT_KV) { warps_meet(1); warps_meet(2); }
+      if (kMeetRefill) { if (lane == 0) refill_at_meeting(it); warps_meet(3); }
     } else {
       const float alpha = tm->alpha, beta = tm->beta, k_mul = tm->k_mul, q_mul = tm->q_mul, kq = tm->kq;
       const float* sscale = reinterpret_cast<const float*>(sb + L::kSScale);
@@ -609,55 +631,68 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
             sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
           }
-          if (cg == 0)
-            *reinterpret_cast<float4*>(sb + L::kSScale + r0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
         }
         PROF_MARK(3)
+        if (cg == 0) stg_v4(dst_sscale + r0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
+                                                            __float_as_uint(snew[2]), __float_as_uint(snew[3])));
+        if constexpr (!kMeetRefill) {
+          // every read of this stage is done: the warp that sees that last refills it with tile it + S
+          __syncwarp();
+          if (lane == 0 && it + S < my_tiles) {
+            __threadfence_block();
+            if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
+              __threadfence_block();
+              done_cnt[s] = 0;
+              load_tile(it + S);
+            }
+          }
+        }
 
-        // phase 3: state codes, new residual (target - code * scale as one fused multiply-add)
+        // phase 3: state codes, new residual.  target - code * scale is one fused multiply-add, which is
+        // exact here (the difference of two nearly equal numbers), so the target can be rebuilt from the
+        // remainder when a row has to be re-decided.  No branch until all four rows are done.
         float eamax[4];
+        uint32_t cw[4][4];
+        float worst = -1.0f;                 // max over rows of (largest remainder - tie guard)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 inv2 = splat(sinv[i]), ns2 = splat(-snew[i]);
-          const float thr = snew[i] * kTieGuard;
-          float em = 0.f;
-          uint32_t packed[4];
+          float emA = 0.f, emB = 0.f;
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {           // 8 elements at a time keeps the temporaries small
-            float2 yE[2], yO[2], eE[2], eO[2];
-            float em8 = 0.f;
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int m = 2 * hf + j;
-              yE[j] = fma2(hE[i][m], inv2, magic2);
-              yO[j] = fma2(hO[i][m], inv2, magic2);
-              eE[j] = fma2(add2(yE[j], nmagic2), ns2, hE[i][m]);
-              eO[j] = fma2(add2(yO[j], nmagic2), ns2, hO[i][m]);
-              em8 = max3abs(max3abs(em8, eE[j]), eO[j]);
-            }
-            if (em8 > thr) {                   // rare: a quotient within the tie guard somewhere in these 8
-              em8 = 0.f;
-#pragma unroll
-              for (int j = 0; j < 2; ++j) {
-                const int m = 2 * hf + j;
-                redecide(hE[i][m].x, eE[j].x, yE[j].x, snew[i], thr); redecide(hE[i][m].y, eE[j].y, yE[j].y, snew[i], thr);
-                redecide(hO[i][m].x, eO[j].x, yO[j].x, snew[i], thr); redecide(hO[i][m].y, eO[j].y, yO[j].y, snew[i], thr);
-                em8 = max3abs(max3abs(em8, eE[j]), eO[j]);
-              }
-            }
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-              const int m = 2 * hf + j;
-              packed[m] = pack4(__float_as_uint(yE[j].x), __float_as_uint(yO[j].x), __float_as_uint(yE[j].y),
-                                __float_as_uint(yO[j].y));
-              hE[i][m] = eE[j]; hO[i][m] = eO[j];
-            }
-            em = fmaxf(em, em8);
+          for (int m = 0; m < 4; ++m) {
+            const float2 yE = fma2(hE[i][m], inv2, magic2);
+            const float2 yO = fma2(hO[i][m], inv2, magic2);
+            hE[i][m] = fma2(add2(yE, nmagic2), ns2, hE[i][m]);
+            hO[i][m] = fma2(add2(yO, nmagic2), ns2, hO[i][m]);
+            emA = max3abs(emA, hE[i][m]);
+            emB = max3abs(emB, hO[i][m]);
+            cw[i][m] = pack4(__float_as_uint(yE.x), __float_as_uint(yO.x), __float_as_uint(yE.y), __float_as_uint(yO.y));
           }
-          *reinterpret_cast<uint4*>(sb + L::kCodes + (r0 + i) * kT + c0) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
-          eamax[i] = em;
+          eamax[i] = fmaxf(emA, emB);
+          worst = fmaxf(worst, fmaf(-snew[i], kTieGuard, eamax[i]));
         }
+        if (worst > 0.f) {                   // rare: some quotient within the tie guard
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float thr = snew[i] * kTieGuard;
+            if (eamax[i] > thr) {
+              float em = 0.f;
+#pragma unroll
+              for (int m = 0; m < 4; ++m) {
+                float2 yE = add2(s8x2_to_float<0, 2>(cw[i][m] ^ 0x80808080u), magic2);
+                float2 yO = add2(s8x2_to_float<1, 3>(cw[i][m] ^ 0x80808080u), magic2);
+                redecide_rec(hE[i][m].x, yE.x, snew[i], thr); redecide_rec(hE[i][m].y, yE.y, snew[i], thr);
+                redecide_rec(hO[i][m].x, yO.x, snew[i], thr); redecide_rec(hO[i][m].y, yO.y, snew[i], thr);
+                em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
+                cw[i][m] = pack4(__float_as_uint(yE.x), __float_as_uint(yO.x), __float_as_uint(yE.y), __float_as_uint(yO.y));
+              }
+              eamax[i] = em;
+            }
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          stg_v4(dst_codes + (r0 + i) * kT + c0, make_uint4(cw[i][0], cw[i][1], cw[i][2], cw[i][3]));
         PROF_MARK(4)
 
         // phase 4: residual scale and codes
@@ -675,8 +710,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         } else {
           const float m4 = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
-          if (lane == 0) head_red[it & 1][warp] = m4;
-          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          if (lane == 0) { head_red[it & 1][warp] = m4; refill_at_meeting(it); }
+          warps_meet(3);
           PROF_MARK(5)
           float m = head_red[it & 1][0];
 #pragma unroll
@@ -705,7 +740,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             }
             const uint32_t w0 = pack4(by[0], by[1], by[2], by[3]) ^ 0x88888888u;
             const uint32_t w1 = pack4(by[4], by[5], by[6], by[7]) ^ 0x88888888u;
-            *reinterpret_cast<uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2) = make_uint2(w0, w1);
+            stg_v2(dst_resid + (r0 + i) * (kT / 2) + c0 / 2, make_uint2(w0, w1));
           } else {
             uint32_t packed[4];
 #pragma unroll
@@ -715,17 +750,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
               packed[m] = pack4(__float_as_uint(ye.x), __float_as_uint(yo.x), __float_as_uint(ye.y),
                                 __float_as_uint(yo.y));
             }
-            *reinterpret_cast<uint4*>(sb + L::kResid + (r0 + i) * kT + c0) =
-                make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            stg_v4(dst_resid + (r0 + i) * kT + c0, make_uint4(packed[0], packed[1], packed[2], packed[3]));
           }
         }
         if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
-          *reinterpret_cast<float4*>(sb + L::kRScale + r0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
-        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) {
-          float* dst = p.packed ? p.rscale_out + (long long)slot * p.stride_rscale_slot + hv
-                                : p.rscale_out + (long long)n * p.HV + hv;
-          *dst = esn[0];
-        }
+          stg_v4(dst_rscale + r0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
+                                                 __float_as_uint(esn[2]), __float_as_uint(esn[3])));
+        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
       } else {
         // ---------------- statequant layout [K][V]: lane = 4 columns x 16 rows ----
         // columns {c0, c0+1} are held as pair A, {c0+2, c0+3} as pair B
@@ -764,7 +795,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           float4* dst = reinterpret_cast<float4*>(red_dot + ((size_t)warp * kT + c0) * 2);
           dst[0] = make_float4(dkA.x, dqA.x, dkA.y, dqA.y);
           dst[1] = make_float4(dkB.x, dqB.x, dkB.y, dqB.y);
-          warps_meet(&meet_bar[0], meet_parity, lane, poison, p.status);
+          warps_meet(1);
 #pragma unroll
           for (int b = 0; b < 4; ++b) { dk[b] = 0.f; dq[b] = 0.f; }
 #pragma unroll
@@ -811,7 +842,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           for (int b = 0; b < 4; ++b) store_from_float(p.out, out_off + c0 + b, p.o_dtype, oval[b]);
         }
         *reinterpret_cast<float4*>(red_max + (size_t)warp * kT + c0) = make_float4(amax[0], amax[1], amax[2], amax[3]);
-        warps_meet(&meet_bar[1], meet_parity, lane, poison, p.status);
+        warps_meet(2);
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
           const float4 x = *reinterpret_cast<const float4*>(red_max + (size_t)w * kT + c0);
@@ -849,12 +880,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
 #pragma unroll
-        for (int i = 0; i < 16; ++i) *reinterpret_cast<uint32_t*>(sb + L::kCodes + (r0 + i) * kT + c0) = cw[i];
+        for (int i = 0; i < 16; ++i) stg_b32(dst_codes + (r0 + i) * kT + c0, cw[i]);
         float esn[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
           *reinterpret_cast<float4*>(red_emax + (size_t)warp * kT + c0) =
               make_float4(eamax[0], eamax[1], eamax[2], eamax[3]);
-          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          if (lane == 0) refill_at_meeting(it);
+          warps_meet(3);
 #pragma unroll
           for (int w = 0; w < kWarps; ++w) {
             const float4 x = *reinterpret_cast<const float4*>(red_emax + (size_t)w * kT + c0);
@@ -865,8 +897,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           for (int b = 0; b < 4; ++b) esn[b] = scale_from_amax(eamax[b], rqmax, p.eps_mode);
         } else {
           float m = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
-          if (lane == 0) head_red[it & 1][warp] = m;
-          warps_meet(&meet_bar[2], meet_parity, lane, poison, p.status);
+          if (lane == 0) { head_red[it & 1][warp] = m; refill_at_meeting(it); }
+          warps_meet(3);
           m = head_red[it & 1][0];
 #pragma unroll
           for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
@@ -881,62 +913,34 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           const uint32_t y2 = __float_as_uint(rB.x), y3 = __float_as_uint(rB.y);
           if constexpr (RES == CARRY_RES_INT4) {
             const uint32_t v16 = (y0 & 0xFu) | ((y1 & 0xFu) << 4) | ((y2 & 0xFu) << 8) | ((y3 & 0xFu) << 12);
-            *reinterpret_cast<uint16_t*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2) = (uint16_t)v16;
+            stg_b16(dst_resid + (r0 + i) * (kT / 2) + c0 / 2, v16);
           } else {
-            *reinterpret_cast<uint32_t*>(sb + L::kResid + (r0 + i) * kT + c0) = pack4(y0, y1, y2, y3);
+            stg_b32(dst_resid + (r0 + i) * kT + c0, pack4(y0, y1, y2, y3));
           }
         }
         // scales: every warp holds all 128 of them; warp w publishes its 16-column share
         // (columns 16w..16w+15 are held by lanes 4w..4w+3)
         if ((lane >> 2) == warp) {
-          *reinterpret_cast<float4*>(sb + L::kSScale + c0 * 4) = make_float4(snew[0], snew[1], snew[2], snew[3]);
+          stg_v4(dst_sscale + c0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
+                                                 __float_as_uint(snew[2]), __float_as_uint(snew[3])));
           if (RSCALE == CARRY_SCALE_PER_V)
-            *reinterpret_cast<float4*>(sb + L::kRScale + c0 * 4) = make_float4(esn[0], esn[1], esn[2], esn[3]);
+            stg_v4(dst_rscale + c0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
+                                                   __float_as_uint(esn[2]), __float_as_uint(esn[3])));
         }
-        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) p.rscale_out[(long long)n * p.HV + hv] = esn[0];
+        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
       }
     }
-    if (live) meet_parity ^= 1u;
     PROF_MARK(6)
 
-    // ---- this warp's 16 rows go back: lanes 0..3 each issue one bulk store ------------
-    __syncwarp();
-    fence_async_smem();
-    __syncwarp();
-    PROF_MARK(7)
-    constexpr int kStorers = (RSCALE == CARRY_SCALE_PER_V) ? 4 : 3;
-    const bool recycle = it > 0 && it - 1 + S < my_tiles;
-    if (lane < kStorers) {
-      if (live && !*poison) {
-        const StoreDesc d = store_tab[lane];
-        const long long major = p.packed ? (long long)slot : (long long)n * p.HV + hv;
-        const long long minor = p.packed ? (long long)hv : 0;
-        bulk_store(reinterpret_cast<void*>(d.base + major * d.major + minor * d.minor + (long long)warp * d.row),
-                   sb + d.src + warp * d.row, (uint32_t)d.row);
-      }
-      bulk_commit();
-      if (recycle) bulk_wait_read<1>();     // the previous tile's stores have left shared memory
-    }
-    PROF_MARK(8)
-    // Stage (it-1) % S is free once every warp's stores of tile it-1 have left
-    // shared memory.  The warp that observes this last refills the stage, so
-    // nobody waits here.
-    if (recycle) {
+    // a skipped tile (padding slot) still has to hand its stage on
+    if (!kMeetRefill && !live && it + S < my_tiles) {
       __syncwarp();
       if (lane == 0) {
         __threadfence_block();
-        const int prev = (it - 1) % S;
-        if (atomicAdd(&done_cnt[prev], 1) == kWarps - 1) {
+        if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
           __threadfence_block();
-          done_cnt[prev] = 0;
-          if (!*poison) {
-            const int nit = it - 1 + S;
-            int tn, thv, tslot;
-            if (nit < kTileCache) { tn = meta_cache[nit].n; thv = meta_cache[nit].hv; tslot = meta_cache[nit].slot; }
-            else { const int tile = (int)blockIdx.x + nit * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
-                   tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
-            issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, prev, tn, thv, tslot);
-          }
+          done_cnt[s] = 0;
+          if (healthy) load_tile(it + S);
         }
       }
     }
@@ -947,7 +951,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     for (int k = 0; k < 12; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.prof) + k, (unsigned long long)prof_acc[k]);
   }
 #endif
-  if (lane < 4) bulk_wait_read<0>();
   __syncthreads();
 }
 
