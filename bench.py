@@ -58,8 +58,9 @@ assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
 # kernel on this workload (64 requests), from the ncu capture summarised under
-# profiles/; None until a capture exists.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# profiles/gdn_tile128_int4_perhead_bf16_b64.md (mean of six steady-state launches, ncu with
+# --cache-control none so that the write-back of the results is inside the window).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 104_740_000
 
 
 def parse_args():
@@ -75,6 +76,9 @@ def parse_args():
                     help="one residual scale per head (the named workload) or per V row")
     ap.add_argument("--warm-steps", type=int, default=WARM_STEPS,
                     help="untimed steps that build the initial state (64 = the named workload)")
+    ap.add_argument("--min-sample-s", type=float, default=0.5,
+                    help="keep replaying after the timed region until the clock sampler has run this long "
+                         "(0 for profiler runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
@@ -433,8 +437,8 @@ def main():
     sampler.start()
     elapsed = time_graph(graph, args.steps, device)
     # keep the sampler alive long enough for at least a few samples under load
-    if elapsed < 0.5:
-        reps = int(0.5 / max(elapsed / args.steps, 1e-6)) + 1
+    if elapsed < args.min_sample_s:
+        reps = int(args.min_sample_s / max(elapsed / args.steps, 1e-6)) + 1
         time_graph(graph, reps, device)
     clocks = sampler.stop()
     if world > 1:
@@ -469,7 +473,8 @@ def main():
                          "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "frac_of_8000": achieved / 8000.0,
                          "bytes_per_launch": SLOT_LAYER_BYTES * args.batch,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.resid == "int4" and args.batch == BATCH
+                                                                     and args.resid_scale == "head") else None,
                          "kernel": {1: "gdn_generic_kernel", 2: "gdn_tile128_kernel"}.get(kernel_used, "?")},
             "cpu_baseline": cpu_base, "parity": parity_stats, "e2e": e2e,
             "gpu_launches": args.steps * args.layers, "clocks": clocks,
