@@ -110,14 +110,39 @@ class Workload:
         slots = max(POOL_SLOTS, batch) + 1
         self.num_slots = slots
         self.pools, self.indices, self.mixed, self.a, self.b, self.out = [], [], [], [], [], []
-        for _ in range(layers):
+        # activations of all layers in one device buffer, outputs in another (per-layer views into
+        # them), so that the host-buffer path can move a group of layers with one copy
+        def up(x):
+            return (x + 255) // 256 * 256
+        seg = [("mixed", (batch, width), torch.bfloat16), ("a", (batch, HV), torch.bfloat16),
+               ("b", (batch, HV), torch.bfloat16), ("idx", (batch,), torch.int32)]
+        self.in_layer_bytes = sum(up(math.prod(shape) * torch.empty((), dtype=dt).element_size()) for _, shape, dt in seg)
+        self.out_layer_bytes = up(batch * HV * V * 2)
+        self.in_dev = torch.zeros(layers * self.in_layer_bytes, dtype=torch.uint8, device=device)
+        self.out_dev = torch.zeros(layers * self.out_layer_bytes, dtype=torch.uint8, device=device)
+        self.in_bytes_useful = layers * sum(math.prod(shape) * torch.empty((), dtype=dt).element_size()
+                                            for _, shape, dt in seg)
+        self.out_bytes_useful = layers * batch * HV * V * 2
+
+        def view(buf, off, shape, dt):
+            n = math.prod(shape) * torch.empty((), dtype=dt).element_size()
+            return buf[off:off + n].view(dt).view(shape)
+
+        for l in range(layers):
             self.pools.append(qpd.init_quantized_state(slots, HV, V, K, device,
                                                        resid_fmt=self.resid_fmt, resid_scale=resid_scale))
-            self.indices.append((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32).to(device))
-            self.mixed.append(torch.randn(batch, width, generator=g).to(torch.bfloat16).to(device))
-            self.a.append(torch.randn(batch, HV, generator=g).to(torch.bfloat16).to(device))
-            self.b.append(torch.randn(batch, HV, generator=g).to(torch.bfloat16).to(device))
-            self.out.append(torch.empty(batch, 1, HV, V, dtype=torch.bfloat16, device=device))
+            off = l * self.in_layer_bytes
+            views = {}
+            for name, shape, dt in seg:
+                views[name] = view(self.in_dev, off, shape, dt)
+                off += up(math.prod(shape) * torch.empty((), dtype=dt).element_size())
+            views["idx"].copy_((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32))
+            views["mixed"].copy_(torch.randn(batch, width, generator=g).to(torch.bfloat16))
+            views["a"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
+            views["b"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
+            self.indices.append(views["idx"]); self.mixed.append(views["mixed"])
+            self.a.append(views["a"]); self.b.append(views["b"])
+            self.out.append(view(self.out_dev, l * self.out_layer_bytes, (batch, 1, HV, V), torch.bfloat16))
         self.A_log = torch.full((HV,), math.log(0.1), device=device)
         self.dt_bias = torch.zeros(HV, device=device)
         self.scale = K ** -0.5
@@ -216,39 +241,61 @@ def time_graph(graph, steps, device):
     return start.elapsed_time(end) * 1e-3
 
 
-def e2e_run(wl, steps, warmup):
-    """The same step through the public call with HOST buffers: every layer's
-    activations and slot ids are copied from pinned host memory, the layer is
-    launched, and its output row block is copied back to pinned host memory;
-    the step ends with a stream synchronise (the host holds every output)."""
+def e2e_run(wl, steps, warmup, groups=4):
+    """The same step through the public call with HOST buffers.  Every step copies all activations and
+    slot ids from pinned host memory to the device, runs the 24 layer calls, and copies every output
+    row back to pinned host memory; the step ends when the host holds all outputs (stream
+    synchronise).  Layers move in `groups` groups: while one group computes (a CUDA graph of its layer
+    calls, captured through the public function), the next group's inputs are already on their way in
+    and the previous group's outputs on their way out, each on its own stream.  The state pools stay
+    in HBM between steps: they are the recurrent state."""
     dev = wl.device
     L = wl.layers
-    host_in = [[t.cpu().pin_memory() for t in (wl.mixed[l], wl.a[l], wl.b[l], wl.indices[l])] for l in range(L)]
-    host_out = [torch.empty(wl.out[l].shape, dtype=wl.out[l].dtype).pin_memory() for l in range(L)]
-    dev_in = [[torch.empty_like(t, device=dev) for t in host_in[l]] for l in range(L)]
-    h2d = sum(t.numel() * t.element_size() for t in host_in[0]) * L
-    d2h = host_out[0].numel() * host_out[0].element_size() * L
+    groups = max(1, min(groups, L))
+    bounds = [(L * g // groups, L * (g + 1) // groups) for g in range(groups)]
+    in_host = wl.in_dev.cpu().pin_memory()
+    out_host = torch.empty(wl.out_dev.shape, dtype=torch.uint8).pin_memory()
+    s_in, s_run, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    graphs = []
+    torch.cuda.synchronize(dev)
+    for lo, hi in bounds:
+        with torch.cuda.stream(s_run):
+            for l in range(lo, hi):
+                wl.layer_step(l)
+        torch.cuda.synchronize(dev)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s_run):
+            for l in range(lo, hi):
+                wl.layer_step(l)
+        graphs.append(g)
+    ev_in = [torch.cuda.Event() for _ in bounds]
+    ev_run = [torch.cuda.Event() for _ in bounds]
 
     def one_step():
-        for l in range(L):
-            for d, h in zip(dev_in[l], host_in[l]):
-                d.copy_(h, non_blocking=True)
-            wl.layer_step(l, *dev_in[l][:3], idx=dev_in[l][3])
-            host_out[l].copy_(wl.out[l], non_blocking=True)
+        for gi, (lo, hi) in enumerate(bounds):
+            a, b = lo * wl.in_layer_bytes, hi * wl.in_layer_bytes
+            with torch.cuda.stream(s_in):
+                wl.in_dev[a:b].copy_(in_host[a:b], non_blocking=True)
+                ev_in[gi].record(s_in)
+            with torch.cuda.stream(s_run):
+                s_run.wait_event(ev_in[gi])
+                graphs[gi].replay()
+                ev_run[gi].record(s_run)
+            a, b = lo * wl.out_layer_bytes, hi * wl.out_layer_bytes
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_run[gi])
+                out_host[a:b].copy_(wl.out_dev[a:b], non_blocking=True)
         torch.cuda.synchronize(dev)
 
     for _ in range(warmup):
         one_step()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     t0 = time.perf_counter()
-    start.record()
     for _ in range(steps):
         one_step()
-    end.record()
     torch.cuda.synchronize(dev)
     wall = time.perf_counter() - t0
-    return max(wall, start.elapsed_time(end) * 1e-3), h2d, d2h
+    return wall, wl.in_bytes_useful, wl.out_bytes_useful
 
 
 # ---------------------------------------------------------------------------
