@@ -11,6 +11,10 @@ The bar (fp32 accumulate on both sides):
   so its code may move across the whole grid;
 * ``o`` and the dequantised state within ``rtol 1e-3 / atol 1e-4``; at a flipped
   element the dequantised state may be off by one state step;
+* a V channel whose whole new residual is below 0.1 % of a state step (the
+  target happened to be representable almost exactly) carries nothing but fp32
+  rounding noise in its residual; there the residual codes and scale are not
+  compared, only the dequantised value;
 * state scales within ``rtol 1e-5``; residual scales within ``rtol 5e-4``: the
   new residual is ``target - code*scale``, a difference of nearly equal numbers,
   so one unit in the last place of the state scale (3e-7 relative, from the
@@ -100,11 +104,18 @@ def check_quant_step(got, ref, res_fmt, unpack_int4=None, int_formats=(3, 4),
         assert e_g is None
         return stats
     if res_fmt in int_formats:
-        torch.testing.assert_close(es_g, es_r, rtol=RESID_SCALE_RTOL, atol=1e-30, msg=f"{what}: residual scale")
+        rq = 7.0 if res_fmt == 4 else 127.0
+        per_v = es_r.dim() == s_r.dim()
+        s_chan = s_r if per_v else s_r.amax(dim=-1)
+        noise = (es_r * rq) < 1e-3 * s_chan                  # residual of this channel is rounding noise
+        ok = ((es_g - es_r).abs() <= RESID_SCALE_RTOL * es_r) | noise
+        assert bool(ok.all()), f"{what}: residual scale off in {int((~ok).sum())} channels"
         if res_fmt == 4:
             e_gc, e_rc = unpack_int4(e_g), unpack_int4(e_r)
         else:
             e_gc, e_rc = e_g, e_r
+        noise_b = (noise[..., None, :] if per_v else noise[..., None, None]).expand_as(flip)
+        flip = flip | noise_b
         # A flipped state code moves that element's residual across the grid, so
         # those elements are left out.  Its magnitude stays ~half a state step, so
         # the residual scale of its column (or head) moves only in the last bits.
@@ -128,8 +139,12 @@ def check_pool(got, ref, int4: bool, slots, unpack_int4, what="pool", max_frac=M
     idx = torch.as_tensor(slots, dtype=torch.long)
     torch.testing.assert_close(ss_g[idx], ss_r[idx], rtol=STATE_SCALE_RTOL, atol=1e-30,
                                msg=f"{what}: state scale")
-    torch.testing.assert_close(rs_g[idx], rs_r[idx], rtol=RESID_SCALE_RTOL, atol=1e-30,
-                               msg=f"{what}: residual scale")
+    rq = 7.0 if int4 else 127.0
+    per_v = rs_r.dim() == 3
+    s_chan = ss_r[idx] if per_v else ss_r[idx].amax(dim=-1)
+    noise = (rs_r[idx] * rq) < 1e-3 * s_chan                 # residual of this channel is rounding noise
+    ok = ((rs_g[idx] - rs_r[idx]).abs() <= RESID_SCALE_RTOL * rs_r[idx]) | noise
+    assert bool(ok.all()), f"{what}: residual scale off in {int((~ok).sum())} channels"
     flip, f_state = assert_codes(sc_g[idx], sc_r[idx], f"{what}: state codes", max_frac)
     s_b = ss_r[idx][..., None]
     assert_close(sc_g[idx].float() * ss_g[idx][..., None], sc_r[idx].float() * s_b,
@@ -137,10 +152,11 @@ def check_pool(got, ref, int4: bool, slots, unpack_int4, what="pool", max_frac=M
     rg, rr = rc_g[idx], rc_r[idx]
     if int4:
         rg, rr = unpack_int4(rg), unpack_int4(rr)
-    _, f_resid = assert_codes(rg, rr, f"{what}: residual codes", max_frac, exclude=flip)
+    noise_b = (noise[..., None] if per_v else noise[..., None, None]).expand_as(flip)
+    _, f_resid = assert_codes(rg, rr, f"{what}: residual codes", max_frac, exclude=flip | noise_b)
     # the dequantised residual itself: half a residual step at most
     rs_b = rs_r[idx][..., None] if rs_r.dim() == 3 else rs_r[idx][..., None, None]
     rs_gb = rs_g[idx][..., None] if rs_g.dim() == 3 else rs_g[idx][..., None, None]
     assert_close(rg.float() * rs_gb, rr.float() * rs_b, f"{what}: dequantised residual",
-                 atol=1e-6, slack=rs_b.expand_as(rr) * 1.001, exclude=flip)
+                 atol=1e-6, slack=rs_b.expand_as(rr) * 1.001, exclude=flip & ~noise_b)
     return f_state, f_resid
