@@ -12,11 +12,15 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 }  // namespace
 
 // The streaming kernel needs K = V = 128, an integer residual, a per-V state
-// scale, and 16-byte aligned, dense rows for every bulk copy.
+// scale, qmax = 2^(bits-1) - 1 for 3..8 bits, and 16-byte aligned, dense rows for every bulk copy.
 bool tile128_eligible(const KParams& p) {
   if (p.K != 128 || p.V != 128) return false;
   if (p.res_fmt != CARRY_RES_INT8 && p.res_fmt != CARRY_RES_INT4) return false;
   if (p.sscale_mode != CARRY_SCALE_PER_V) return false;
+  // the kernel divides by qmax with a multiply and a correcting fused multiply-add, which equals the
+  // IEEE quotient for these values (the quantisation widths 3..8 bits) and has not been checked for others
+  if (p.qmax != 3.f && p.qmax != 7.f && p.qmax != 15.f && p.qmax != 31.f && p.qmax != 63.f && p.qmax != 127.f)
+    return false;
   if (p.HV > 128 || (long long)p.B * p.HV > 0x7fffffffLL) return false;
   const int qes = p.qkv_dtype == CARRY_F32 ? 4 : 2;
   if (!aligned16(p.codes_in) || !aligned16(p.codes_out) || !aligned16(p.resid_in) || !aligned16(p.resid_out) ||

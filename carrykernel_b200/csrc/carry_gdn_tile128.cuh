@@ -163,26 +163,76 @@ __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, ui
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
 }
 
-__device__ __forceinline__ float warp_sum8(float x) {   // over the 8 lanes sharing a row group
-  x += __shfl_xor_sync(0xffffffffu, x, 1);
-  x += __shfl_xor_sync(0xffffffffu, x, 2);
-  x += __shfl_xor_sync(0xffffffffu, x, 4);
-  return x;
+// max of a non-negative float over the whole warp: for non-negative floats the order of the bit
+// patterns is the order of the values, so the integer warp reduction does it in one instruction.
+// (Only with the full mask: a reduction over part of a warp costs some 300 cycles on sm_100.)
+__device__ __forceinline__ float warp_max_nonneg(float x) {
+  return __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(x)));
 }
-__device__ __forceinline__ float warp_max8(float x) {
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
-  return x;
+
+// Four values per lane, each to be maximised over the 8 lanes of a row group.  Halving exchange: lane g
+// of the group ends up with the maximum of x[(g >> 1) & 3], at 4 shuffles instead of 12.
+__device__ __forceinline__ float group_max4_transposed(const float (&x)[4], int g) {
+  const bool up4 = g & 4, up2 = g & 2;
+  float a[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float keep = up4 ? x[2 + i] : x[i], send = up4 ? x[i] : x[2 + i];
+    a[i] = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 4));
+  }
+  const float keep = up2 ? a[1] : a[0], send = up2 ? a[0] : a[1];
+  const float b = fmaxf(keep, __shfl_xor_sync(0xffffffffu, send, 2));
+  return fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 1));
 }
+
+// 1/s to within 2^-24 (1 + 2^-20) relative: the hardware approximation (1 ulp) and one Newton step.  The
+// rounding routine only needs the reciprocal that close -- quotients that the difference could tip over a
+// tie are caught by the tie guard and re-decided by a true division -- and this is a third of the
+// latency of the correctly rounded routine.  s is a scale: normal, between 1e-12 and 1e37.
+__device__ __forceinline__ float rcp_refined(float s) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(s));
+  return fmaf(y, fmaf(-s, y, 1.0f), y);
+}
+
+// Eight values per lane (x[0..3], y[0..3]), each to be summed over the 8 lanes of a row group.
+// Halving exchange: after three rounds lane g of the group holds one total -- x[g] for g < 4,
+// y[g - 4] otherwise -- at 7 shuffles instead of 24.
+__device__ __forceinline__ float group_sum8_transposed(const float (&x)[4], const float (&y)[4], int g) {
+  const bool up4 = g & 4, up2 = g & 2, up1 = g & 1;
+  float a[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float keep = up4 ? y[i] : x[i], send = up4 ? x[i] : y[i];
+    a[i] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+  }
+  float b[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const float keep = up2 ? a[2 + i] : a[i], send = up2 ? a[i] : a[2 + i];
+    b[i] = keep + __shfl_xor_sync(0xffffffffu, send, 2);
+  }
+  const float keep = up1 ? b[1] : b[0], send = up1 ? b[0] : b[1];
+  return keep + __shfl_xor_sync(0xffffffffu, send, 1);
+}
+
+// amax / qmax, correctly rounded, without the division routine.  `rq` is 1/qmax rounded to nearest;
+// a * rq is within an ulp of the quotient, the remainder a - qmax * q0 is exact in one fused
+// multiply-add and corrects it.  Equal to IEEE division for every float a >= 2^-100 when qmax is one of
+// 3, 7, 15, 31, 63, 127 (checked over every mantissa; tests/test_host_api.py repeats the check), and the
+// launcher admits no other qmax.  Smaller a end at the 1e-12 floor either way.
+__device__ __forceinline__ float div_qmax(float a, float qmax, float rq) {
+  const float q0 = __fmul_rn(a, rq);
+  return fmaf(fmaf(-qmax, q0, a), rq, q0);
+}
+__device__ __forceinline__ float scale_fast(float amax, float qmax, float rq, int eps_mode) {
+  if (eps_mode == CARRY_EPS_ON_AMAX) return div_qmax(fmaxf(amax, kEps), qmax, rq);
+  return fmaxf(div_qmax(amax, qmax, rq), kEps);
+}
+
 __device__ __forceinline__ float warp_sum32(float x) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-  return x;
-}
-__device__ __forceinline__ float warp_max32(float x) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
   return x;
 }
 
@@ -292,7 +342,7 @@ __device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float 
 }
 
 // gates of one (request, head): derived in the kernel on the slot path, given on the other
-__device__ __noinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta) {
+__device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta) {
   if (p.packed) {
     slot_gates(load_as_float(p.a, (long long)n * p.stride_a_tok + hv, p.ab_dtype),
                load_as_float(p.b, (long long)n * p.stride_b_tok + hv, p.ab_dtype),
@@ -305,21 +355,25 @@ __device__ __noinline__ void gates_of(const KParams& p, int n, int hv, float& al
 }
 
 // What a CTA needs to know about one of its tiles before the data arrives.
-struct TileMeta {
+struct __align__(16) TileMeta {
   int n, hv, slot;
   float alpha, beta;
   float k_mul, q_mul;   // 1/|k| and scale/|q| (1 when the L2 norm is off or on the statequant path)
   float kq;             // <k, q> after those factors
 };
+static_assert(sizeof(TileMeta) == 32, "TileMeta is read as two 16-byte words");
 
-// Computed by a whole warp straight from global memory: slot id, gates, and the
-// norms of k and q (4 elements per lane, then warp sums).
-__device__ __noinline__ void tile_meta(const KParams& p, int tile, int lane, TileMeta* dst) {
+// Computed by four consecutive lanes straight from global memory: slot id, gates, and the norms of k
+// and q (32 elements per lane, then a sum over the four lanes).  Every load depends on the tile index
+// alone, so the whole thing is one trip to memory however many tiles a CTA prepares at once.  All 32
+// lanes of a warp must call this together; the first lane of a group writes `dst` when `store` is set.
+template <int QDT>
+__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst) {
+  constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
+  constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
   TileMeta m;
   m.n = tile / p.HV;
   m.hv = tile - m.n * p.HV;
-  m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
-  gates_of(p, m.n, m.hv, m.alpha, m.beta);
   long long q_off, k_off;
   if (p.packed) {
     const int h = m.hv / (p.HV / p.H);
@@ -328,16 +382,35 @@ __device__ __noinline__ void tile_meta(const KParams& p, int tile, int lane, Til
   } else {
     q_off = k_off = ((long long)m.n * p.HV + m.hv) * kT;
   }
+  const uint4* qp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + (q_off + 32 * sub) * qes);
+  const uint4* kp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k) + (k_off + 32 * sub) * qes);
+  uint4 qv[kVecs], kv[kVecs];
+#pragma unroll
+  for (int j = 0; j < kVecs; ++j) { qv[j] = __ldg(qp + j); kv[j] = __ldg(kp + j); }
+  m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
+  gates_of(p, m.n, m.hv, m.alpha, m.beta);
   float ks = 0.f, qs = 0.f, kq = 0.f;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float kv = load_as_float(p.k, k_off + 4 * lane + i, p.qkv_dtype);
-    const float qv = load_as_float(p.q, q_off + 4 * lane + i, p.qkv_dtype);
-    ks = fmaf(kv, kv, ks);
-    qs = fmaf(qv, qv, qs);
-    kq = fmaf(kv, qv, kq);
+  for (int j = 0; j < kVecs; ++j) {
+    const uint32_t qw[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w}, kw[4] = {kv[j].x, kv[j].y, kv[j].z, kv[j].w};
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (QDT == CARRY_F32) {
+        const float a = __uint_as_float(kw[c]), b = __uint_as_float(qw[c]);
+        ks = fmaf(a, a, ks); qs = fmaf(b, b, qs); kq = fmaf(a, b, kq);
+      } else {
+        const float2 a = act_pair<QDT>(kw[c]), b = act_pair<QDT>(qw[c]);
+        ks = fmaf(a.x, a.x, ks); qs = fmaf(b.x, b.x, qs); kq = fmaf(a.x, b.x, kq);
+        ks = fmaf(a.y, a.y, ks); qs = fmaf(b.y, b.y, qs); kq = fmaf(a.y, b.y, kq);
+      }
+    }
   }
-  ks = warp_sum32(ks); qs = warp_sum32(qs); kq = warp_sum32(kq);
+#pragma unroll
+  for (int o = 1; o <= 2; o <<= 1) {
+    ks += __shfl_xor_sync(0xffffffffu, ks, o);
+    qs += __shfl_xor_sync(0xffffffffu, qs, o);
+    kq += __shfl_xor_sync(0xffffffffu, kq, o);
+  }
   m.k_mul = 1.0f; m.q_mul = 1.0f;
   if (p.packed) {
     if (p.l2norm) {
@@ -347,8 +420,7 @@ __device__ __noinline__ void tile_meta(const KParams& p, int tile, int lane, Til
     m.q_mul *= p.qscale;
   }
   m.kq = kq * (m.k_mul * m.q_mul);
-  if (lane == 0) *dst = m;
-  __syncwarp();
+  if (store) *dst = m;
 }
 
 // Load one tile into stage `stage` (called by one thread).
@@ -433,6 +505,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
                 "static shared memory exceeds what the stage ring was sized for");
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef CARRY_PROFILE
+  const long long prof_k0 = clock64();
+  unsigned long long prof_g0;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
+#endif
   const int total = p.B * p.HV;
   const int my_tiles = (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   volatile int* poison = &poison_flag;
@@ -443,23 +520,40 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     first_cnt[0] = first_cnt[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // slot ids, gates and norms of this CTA's first tiles: one trip to global memory, up front
-  for (int i = warp; i < my_tiles && i < kTileCache; i += kWarps)
-    tile_meta(p, (int)blockIdx.x + i * (int)gridDim.x, lane, &meta_cache[i]);
   __syncthreads();
-
-  if (tid == 0) {
-    const int pre = my_tiles < S ? my_tiles : S;
-    for (int it = 0; it < pre; ++it) {
-      int tn, thv, tslot;
-      if (it < kTileCache) { tn = meta_cache[it].n; thv = meta_cache[it].hv; tslot = meta_cache[it].slot; }
-      else { const int tile = (int)blockIdx.x + it * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
-             tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
-      issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, it % S, tn, thv, tslot);
-    }
+#ifdef CARRY_PROFILE
+  const long long prof_p1 = clock64();
+#endif
+  // The first S tiles are requested before anything else: warp i fetches tile i's slot id (the only thing
+  // a request depends on) and issues that tile's copies.  Then all threads gather slot ids, gates and norms
+  // of this CTA's first tiles, four lanes per tile, in one trip to global memory.
+  if (lane == 0 && warp < S && warp < my_tiles) {
+    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
+    const int tn = tile / p.HV, thv = tile - tn * p.HV;
+    const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, warp, tn, thv, tslot);
   }
+  __syncwarp();
+#ifdef CARRY_PROFILE
+  const long long prof_p2 = clock64();
+#endif
+  {
+    static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
+    const int i = tid >> 2;
+    const bool valid = i < my_tiles;
+    tile_meta4<QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid && (tid & 3) == 0,
+                    &meta_cache[i]);
+  }
+#ifdef CARRY_PROFILE
+  const long long prof_p3 = clock64();
+#endif
+  __syncthreads();
+#ifdef CARRY_PROFILE
+  const long long prof_p4 = clock64();
+#endif
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
+  const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
   // Variants whose warps meet once per tile refill a stage one tile late: when tile `it` reaches its
   // last meeting every warp has long left tile it-1, and the first warp to arrive -- the one with the
   // most slack -- loads tile it-1+S into that stage while it waits for the others.  Variants without a
@@ -491,8 +585,12 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const uint32_t parity = (uint32_t)(it / S) & 1u;
     uint8_t* sb = smem + (size_t)s * L::kBytes;
     const TileMeta* tm = &meta_cache[it < kTileCache ? it : kTileCache + warp];
-    if (it >= kTileCache) tile_meta(p, (int)blockIdx.x + it * (int)gridDim.x, lane, &meta_cache[kTileCache + warp]);
-    const int n = tm->n, hv = tm->hv;
+    if (it >= kTileCache) {
+      tile_meta4<QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane == 0, &meta_cache[kTileCache + warp]);
+      __syncwarp();
+    }
+    const uint4 tm0 = lds_v4(tm);
+    const int n = (int)tm0.x, hv = (int)tm0.y;
 
     const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
     PROF_MARK(0)
@@ -511,7 +609,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       if (LAYOUT == LAYOUT_KV) { warps_meet(1); warps_meet(2); }
       if (kMeetRefill) { if (lane == 0) refill_at_meeting(it); warps_meet(3); }
     } else {
-      const float alpha = tm->alpha, beta = tm->beta, k_mul = tm->k_mul, q_mul = tm->q_mul, kq = tm->kq;
+      const uint4 tm1 = lds_v4(reinterpret_cast<const uint8_t*>(tm) + 16);
+      const float alpha = __uint_as_float(tm0.w), beta = __uint_as_float(tm1.x), k_mul = __uint_as_float(tm1.y),
+                  q_mul = __uint_as_float(tm1.z), kq = __uint_as_float(tm1.w);
       const float* sscale = reinterpret_cast<const float*>(sb + L::kSScale);
       const float* rscale = reinterpret_cast<const float*>(sb + L::kRScale);
       const float es_head = (RSCALE == CARRY_SCALE_PER_HEAD) ? rscale[hv] : 0.f;
@@ -524,9 +624,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         const int cg = lane & 7, rg = lane >> 3;
         const int r0 = 16 * warp + 4 * rg, c0 = 16 * cg;
         float* qw = q_warp + warp * kT;
-        {   // this warp's copy of q: fp32, scaled, each quad stored as {q0, q2, q1, q3}
+        {   // this warp's copy of q: fp32, scaled, each quad stored as {q0, q2, q1, q3}.  Quad j = 4 cg + m
+            // sits at position 8 m + cg, so that the 8 lanes of a row group read 128 contiguous bytes.
           const float4 q4 = act4<QDT>(sb + L::kQ, 4 * lane);
-          *reinterpret_cast<float4*>(qw + 4 * lane) = make_float4(q4.x * q_mul, q4.z * q_mul, q4.y * q_mul, q4.w * q_mul);
+          *reinterpret_cast<float4*>(qw + 4 * (8 * (lane & 3) + (lane >> 2))) =
+              make_float4(q4.x * q_mul, q4.z * q_mul, q4.y * q_mul, q4.w * q_mul);
         }
         float2 kE[4], kO[4];
         act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
@@ -538,7 +640,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         {
           const float4 s4 = *reinterpret_cast<const float4*>(sscale + r0);
           const float srow[4] = {s4.x, s4.y, s4.z, s4.w};
-          const uint32_t q_addr = smem_u32(qw + c0);
+          const uint32_t q_addr = smem_u32(qw + 4 * cg);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
@@ -552,7 +654,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
               hE[i][m] = e; hO[i][m] = o;
               float2 qe, qo;       // re-read per row on purpose: q must not stay in registers
               asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(qe.x), "=f"(qe.y), "=f"(qo.x), "=f"(qo.y) : "r"(q_addr + 16 * m));
+                           : "=f"(qe.x), "=f"(qe.y), "=f"(qo.x), "=f"(qo.y) : "r"(q_addr + 128 * m));
               ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
               aq = fma2(e, qe, aq); aq = fma2(o, qo, aq);
             }
@@ -560,8 +662,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
         PROF_MARK(1)
+        // lane cg of a row group ends up with one total: <h row, k> of row cg (cg < 4) or <h row, q> of
+        // row cg - 4; the four k totals are then handed to every lane of the group
+        const float dot_mine = group_sum8_transposed(dk, dq, cg);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { dk[i] = warp_sum8(dk[i]); dq[i] = warp_sum8(dq[i]); }
+        for (int i = 0; i < 4; ++i) dk[i] = __shfl_sync(0xffffffffu, dot_mine, (lane & 24) + i);
         PROF_MARK(2)
 
         // phase 2: rank-1 write and residual, each one fused multiply-add; row maxima
@@ -570,20 +675,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           const float4 v4 = act4<QDT>(sb + L::kV, r0);
           dvr[0] = __fmul_rn(beta, __fadd_rn(v4.x, -dk[0])); dvr[1] = __fmul_rn(beta, __fadd_rn(v4.y, -dk[1]));
           dvr[2] = __fmul_rn(beta, __fadd_rn(v4.z, -dk[2])); dvr[3] = __fmul_rn(beta, __fadd_rn(v4.w, -dk[3]));
-          if (cg == 0) {                      // four consecutive outputs of this lane's rows
-            const float o0 = fmaf(dvr[0], kq, dq[0]), o1 = fmaf(dvr[1], kq, dq[1]);
-            const float o2 = fmaf(dvr[2], kq, dq[2]), o3 = fmaf(dvr[3], kq, dq[3]);
-            if (p.o_dtype == CARRY_F32) {
-              *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + out_off + r0) = make_float4(o0, o1, o2, o3);
-            } else if (p.o_dtype == CARRY_BF16) {
-              const __nv_bfloat162 a = __floats2bfloat162_rn(o0, o1), b = __floats2bfloat162_rn(o2, o3);
-              *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(p.out) + out_off + r0) =
-                  make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-            } else {
-              const __half2 a = __floats2half2_rn(o0, o1), b = __floats2half2_rn(o2, o3);
-              *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(p.out) + out_off + r0) =
-                  make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
-            }
+          if (cg >= 4) {                      // the lanes that hold a q total finish that row's output
+            const int i = cg & 3;
+            const float dv_i = (i == 0) ? dvr[0] : (i == 1) ? dvr[1] : (i == 2) ? dvr[2] : dvr[3];
+            store_from_float(p.out, out_off + r0 + i, p.o_dtype, fmaf(dv_i, kq, dot_mine));
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -618,18 +713,16 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             amax[i] = am;
           }
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) amax[i] = warp_max8(amax[i]);
-        // new state scales: lane cg of a row group does row cg's divisions, then they are shared
+        // new state scales: lanes 2i, 2i+1 of a row group end up with row i's maximum and derive its
+        // scale and reciprocal, which are then handed to the whole group
         float snew[4], sinv[4];
         {
-          const float mine = (cg == 0) ? amax[0] : (cg == 1) ? amax[1] : (cg == 2) ? amax[2] : amax[3];
-          const float s_mine = scale_from_amax(mine, p.qmax, p.eps_mode);
-          const float i_mine = __frcp_rn(s_mine);
+          const float s_mine = scale_fast(group_max4_transposed(amax, cg), p.qmax, rqmax_state, p.eps_mode);
+          const float i_mine = rcp_refined(s_mine);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
-            sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
+            snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + 2 * i);
+            sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + 2 * i);
           }
         }
         PROF_MARK(3)
@@ -698,26 +791,23 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // phase 4: residual scale and codes
         float esn[4], einv[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) eamax[i] = warp_max8(eamax[i]);
-          const float mine = (cg == 0) ? eamax[0] : (cg == 1) ? eamax[1] : (cg == 2) ? eamax[2] : eamax[3];
-          const float s_mine = scale_from_amax(mine, rqmax, p.eps_mode);
-          const float i_mine = __frcp_rn(s_mine);
+          const float s_mine = scale_fast(group_max4_transposed(eamax, cg), rqmax, rrqmax, p.eps_mode);
+          const float i_mine = rcp_refined(s_mine);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
-            esn[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + i);
-            einv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + i);
+            esn[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + 2 * i);
+            einv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + 2 * i);
           }
         } else {
-          const float m4 = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
+          const float m4 = warp_max_nonneg(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
           if (lane == 0) { head_red[it & 1][warp] = m4; refill_at_meeting(it); }
           warps_meet(3);
           PROF_MARK(5)
           float m = head_red[it & 1][0];
 #pragma unroll
           for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
-          const float e1 = scale_from_amax(m, rqmax, p.eps_mode);
-          const float i1 = __frcp_rn(e1);
+          const float e1 = scale_fast(m, rqmax, rrqmax, p.eps_mode);
+          const float i1 = rcp_refined(e1);
 #pragma unroll
           for (int i = 0; i < 4; ++i) { esn[i] = e1; einv[i] = i1; }
         }
@@ -851,9 +941,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
         float snew[4], thr[4];
 #pragma unroll
-        for (int b = 0; b < 4; ++b) { snew[b] = scale_from_amax(amax[b], p.qmax, p.eps_mode); thr[b] = snew[b] * kTieGuard; }
-        const float2 invA = make_float2(__frcp_rn(snew[0]), __frcp_rn(snew[1]));
-        const float2 invB = make_float2(__frcp_rn(snew[2]), __frcp_rn(snew[3]));
+        for (int b = 0; b < 4; ++b) { snew[b] = scale_fast(amax[b], p.qmax, rqmax_state, p.eps_mode); thr[b] = snew[b] * kTieGuard; }
+        const float2 invA = make_float2(rcp_refined(snew[0]), rcp_refined(snew[1]));
+        const float2 invB = make_float2(rcp_refined(snew[2]), rcp_refined(snew[3]));
         const float2 nsA = make_float2(-snew[0], -snew[1]), nsB = make_float2(-snew[2], -snew[3]);
         float eamax[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t cw[16];
@@ -894,18 +984,18 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             eamax[2] = fmaxf(eamax[2], x.z); eamax[3] = fmaxf(eamax[3], x.w);
           }
 #pragma unroll
-          for (int b = 0; b < 4; ++b) esn[b] = scale_from_amax(eamax[b], rqmax, p.eps_mode);
+          for (int b = 0; b < 4; ++b) esn[b] = scale_fast(eamax[b], rqmax, rrqmax, p.eps_mode);
         } else {
-          float m = warp_max32(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
+          float m = warp_max_nonneg(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
           if (lane == 0) { head_red[it & 1][warp] = m; refill_at_meeting(it); }
           warps_meet(3);
           m = head_red[it & 1][0];
 #pragma unroll
           for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
-          esn[0] = esn[1] = esn[2] = esn[3] = scale_from_amax(m, rqmax, p.eps_mode);
+          esn[0] = esn[1] = esn[2] = esn[3] = scale_fast(m, rqmax, rrqmax, p.eps_mode);
         }
-        const float2 ieA = make_float2(__frcp_rn(esn[0]), __frcp_rn(esn[1]));
-        const float2 ieB = make_float2(__frcp_rn(esn[2]), __frcp_rn(esn[3]));
+        const float2 ieA = make_float2(rcp_refined(esn[0]), rcp_refined(esn[1]));
+        const float2 ieB = make_float2(rcp_refined(esn[2]), rcp_refined(esn[3]));
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 rA = fma2(hA[i], ieA, magic2), rB = fma2(hB[i], ieB, magic2);
@@ -949,6 +1039,26 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #ifdef CARRY_PROFILE
   if (lane == 0 && p.prof) {
     for (int k = 0; k < 12; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.prof) + k, (unsigned long long)prof_acc[k]);
+    unsigned long long g1;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
+    unsigned long long* pp = reinterpret_cast<unsigned long long*>(p.prof);
+    atomicMax(pp + 80, (unsigned long long)(clock64() - prof_k0));   // longest CTA, cycles
+    atomicMax(pp + 81, g1 - prof_g0);                                 // longest CTA, ns
+    atomicMin(pp + 82, prof_g0);                                      // first start
+    atomicMax(pp + 83, g1);                                           // last end
+    atomicAdd(pp + 84, (unsigned long long)(clock64() - prof_k0));   // sum over warps of kernel cycles
+    if (warp == 0) {
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      pp[96 + 4 * blockIdx.x] = prof_g0;
+      pp[96 + 4 * blockIdx.x + 1] = g1;
+      pp[96 + 4 * blockIdx.x + 2] = smid;
+      pp[96 + 4 * blockIdx.x + 3] = (unsigned long long)prof_acc[0];
+    }
+    atomicAdd(pp + 85, (unsigned long long)(prof_p1 - prof_k0));
+    atomicAdd(pp + 86, (unsigned long long)(prof_p2 - prof_p1));
+    atomicAdd(pp + 87, (unsigned long long)(prof_p3 - prof_p2));
+    atomicAdd(pp + 88, (unsigned long long)(prof_p4 - prof_p3));
   }
 #endif
   __syncthreads();

@@ -171,3 +171,27 @@ def test_packed_decode_validation_messages():
         call(mixed_qkv=torch.zeros(B, HV * V + 3))
     with pytest.raises(qpd.CudaUnavailable):
         call()
+
+
+@pytest.mark.parametrize("qmax", [3, 7, 15, 31, 63, 127])
+def test_scale_division_shortcut_is_exact(qmax):
+    """The streaming kernel computes amax / qmax as q0 = amax * (1/qmax), then
+    fma(fma(-qmax, q0, amax), 1/qmax, q0) (carry_gdn_tile128.cuh, div_qmax).
+    For these qmax that equals the IEEE quotient for every mantissa; float64
+    emulates each float32 FMA here without a second rounding (all products of
+    two float32 are exact in float64, and so are the two sums for operands this
+    close)."""
+    import numpy as np
+    y = np.float32(1.0) / np.float32(qmax)
+    for exp in (-40, 0, 60):                          # the identity does not depend on the binade
+        bits = (np.uint32((exp + 127) << 23) | np.arange(1 << 23, dtype=np.uint32))
+        a = bits.view(np.float32)
+        a64 = a.astype(np.float64)
+        want = (a64 / float(qmax)).astype(np.float32)
+        q0 = (a64 * float(y)).astype(np.float32)
+        r = (a64 - float(qmax) * q0.astype(np.float64)).astype(np.float32)
+        got = (q0.astype(np.float64) + r.astype(np.float64) * float(y)).astype(np.float32)
+        assert np.array_equal(got, want)
+        # float64 division then rounding to float32 is the float32 quotient: a double rounding could
+        # only bite when the float64 quotient sits exactly on a float32 tie, which a/qmax with a 24-bit
+        # a and qmax < 2^7 cannot do unless it is exact
