@@ -5,32 +5,37 @@
 //
 //   global --cp.async.bulk--> shared stage --> registers --16-byte stores--> global
 //
-// Persistent CTAs (two per SM) walk the tile list with a ring of stages: while
-// one tile is computed, the loads of the next ones are in flight.  A stage is
-// handed back as soon as its last byte has been read (before the tile is
-// quantised), and results leave straight from registers as 16-byte vector
-// stores that cover whole 128-byte lines.  The state is read from HBM once and
-// written once.
+// One persistent CTA per SM walks its share of the tile list (tile = blockIdx.x +
+// number * gridDim.x) through a ring of stages: while tiles are computed, the loads
+// of the next ones are in flight.  The CTA holds two groups of 8 warps (one group
+// where a variant needs more than 128 registers per thread); each group works on a
+// whole tile, and the groups take tiles off the CTA's list as they go, because the
+// two do not get equal shares of the SM's issue slots.  A stage is handed back
+// right after the tile's last meeting, when its last byte has been read, and
+// results leave straight from registers as 16-byte vector stores that cover whole
+// 128-byte lines.  The state is read from HBM once and written once.
 //
-// Work split inside a CTA (256 threads = 8 warps): warp w owns memory rows
+// Work split inside a group (256 threads = 8 warps): warp w owns memory rows
 // 16w..16w+15 of the tile.
 //   * slot layout [V][K] (scale per row): lane = (row group rg, column group
 //     cg): 4 rows x 16 contiguous columns.  Everything the math reduces over
-//     (K) lies along the row, so reductions are 3 shuffle steps inside 8 lanes
-//     and warps never wait for each other, except once per tile when the
-//     residual scale is per head.
+//     (K) lies along the row, so reductions are shuffles inside 8 lanes; the
+//     warps meet once per tile (for the per-head residual scale, and to agree on
+//     the next tile).
 //   * statequant layout [K][V] (scale per column): lane = 4 contiguous columns
 //     x the warp's 16 rows; column sums are finished across the 8 warps through
-//     shared memory.
+//     shared memory (three meetings per tile).
 //
-// Arithmetic keeps the reference's operation order for everything that feeds a
-// state code: (code*scale)*alpha, h + (k*dv) with the product rounded first,
-// target - (code*scale) with the product rounded first.  round(target / s) is
-// evaluated as rint(target * (1/s)); the two can only differ when the quotient
-// is within ~8e-6 of a tie, which shows up as a remainder within 2^-16 of half
-// a step -- groups of elements where that happens are re-decided with the true
-// division.  Residual codes use rint(e * (1/es)) as is.  Math runs as packed
-// f32x2 (IEEE round-to-nearest per component).
+// Arithmetic.  Everything that feeds a state code keeps the reference's operation
+// order, with the contractions written out as explicit fused multiply-adds:
+// h = (code*scale)*alpha, h' = fma(k, dv, h), target = fma(resid_code, resid_scale, h'),
+// remainder = fma(code', -scale', target).  Scales are amax / qmax by an exact
+// shortcut (div_qmax).  round(target / s) is evaluated as rint(target * (1/s)) with a
+// reciprocal good to 2^-24; the two can only differ when the quotient is within ~8e-6
+// of a tie, which shows up as a remainder within 2^-16 of half a step -- rows where
+// that happens are re-decided with the true division.  Residual codes use
+// rint(e * (1/es)) as is.  Math runs as packed f32x2 (IEEE round-to-nearest per
+// component).
 #pragma once
 #include "carry_gdn_common.cuh"
 
@@ -38,10 +43,10 @@ namespace carry {
 namespace {
 
 constexpr int kT = 128;                 // tile edge
-constexpr int kThreads = 256;
+constexpr int kThreads = 256;          // threads of one group: the 8 warps that share a tile
 constexpr int kWarps = 8;
 constexpr uint32_t kSpinLimit = 1u << 22;
-constexpr int kTileCache = 64;         // per-CTA cache of slot ids and gates for its first tiles
+constexpr int kTileCache = 64;         // per group: cached slot ids and gates of the CTA's first tiles
 
 enum { LAYOUT_VK = 0, LAYOUT_KV = 1 };  // slot layout [V][K]; statequant layout [K][V]
 
@@ -123,11 +128,11 @@ __device__ __forceinline__ void stg_b16(unsigned long long addr, uint32_t v) {
   asm volatile("st.global.b16 [%0], %1;" ::"l"(addr), "h"((unsigned short)v) : "memory");
 }
 
-// All 8 warps meet on a hardware named barrier.  Every thread of the CTA runs
-// the same number of tile iterations and reaches the same number of meetings in
-// each of them whether or not the tile is live (skipped tiles take them in the
-// else branch), so a meeting cannot be left waiting for a warp that never comes.
-// Waits on data in flight (the stage barriers) are the bounded ones.
+// The 8 warps of a group meet on a hardware named barrier (ids 1..3 for group 0, 4..6 for group 1).
+// Every thread of a group runs the same tiles and reaches the same number of meetings in each of them
+// whether or not the tile is live (skipped tiles take them in the else branch), so a meeting cannot be
+// left waiting for a warp that never comes.  Waits on data in flight (the stage barriers) are the
+// bounded ones.
 __device__ __forceinline__ void warps_meet(int id) { asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(kThreads) : "memory"); }
 
 // ---------------------------------------------------------------------------
@@ -242,10 +247,10 @@ __device__ __forceinline__ float warp_sum32(float x) {
 // Static shared memory next to the stage ring: barriers, the per-CTA tile caches,
 // the per-warp q scratch (slot layout) or the column-reduction space (statequant
 // layout).  Upper bounds, used to size the ring.
-constexpr int kStaticVK = 7168;
+constexpr int kStaticVK = 7168;         // per group
 constexpr int kStaticKV = 19456;
-constexpr int kSmemPerCta2 = 115712;    // (228 KB - 2 x 1 KB reserved) / 2: two CTAs per SM
-constexpr int kSmemPerCta1 = 231424;    // one CTA per SM
+constexpr int kStaticOf(int layout) { return layout == 0 ? kStaticVK : kStaticKV; }
+constexpr int kSmemPerCta = 231424;     // one CTA per SM: 227 KB less 1 KB
 
 template <int RES, int LAYOUT, int QDT>
 struct StageLayout {
@@ -260,16 +265,18 @@ struct StageLayout {
   static constexpr int kV = kK + kVecBytes;
   static constexpr int kHeader = kV + kVecBytes;             // int slot, then the 4 destination pointers
   static constexpr int kBytes = kHeader + 48;
-  static constexpr int kStatic = (LAYOUT == 0) ? kStaticVK : kStaticKV;
-  // two CTAs per SM when at least 3 stages fit next to the static part, else one
-#ifdef CARRY_FORCE_1CTA
-  static constexpr int kCtasPerSm = 1;
+  // Two groups of 8 warps share one CTA (and one SM) when a group's registers allow it -- at least 3
+  // stages per group must fit too -- else the CTA is a single group.
+#ifdef CARRY_FORCE_1GROUP
+  static constexpr int kGroups = 1;
 #else
-  static constexpr int kCtasPerSm = (3 * kBytes + kStatic <= kSmemPerCta2) ? 2 : 1;
+  static constexpr int kGroups =
+      (LAYOUT == 1 && RES != CARRY_RES_INT4) ? 1 : ((6 * kBytes + 2 * kStaticOf(LAYOUT) <= kSmemPerCta) ? 2 : 1);
 #endif
-  static constexpr int kBudget = (kCtasPerSm == 2 ? kSmemPerCta2 : kSmemPerCta1) - kStatic;
+  static constexpr int kStatic = kGroups * kStaticOf(LAYOUT);
+  static constexpr int kBudget = kSmemPerCta - kStatic;
   static constexpr int kFit = kBudget / kBytes;
-  static constexpr int kStages = kFit > 5 ? 5 : kFit;
+  static constexpr int kStages = kFit > 5 * kGroups ? 5 * kGroups : kFit;
 };
 
 __device__ __forceinline__ int esize(int dtype) { return dtype == CARRY_F32 ? 4 : 2; }
@@ -487,28 +494,34 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
 // the kernel
 // ---------------------------------------------------------------------------
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__global__ void __launch_bounds__(kThreads, (StageLayout<RES, LAYOUT, QDT>::kCtasPerSm))
+__global__ void __launch_bounds__(kThreads * StageLayout<RES, LAYOUT, QDT>::kGroups, 1)
 gdn_tile128_kernel(const __grid_constant__ KParams p) {
   using L = StageLayout<RES, LAYOUT, QDT>;
   constexpr int S = L::kStages;
+  constexpr int G = L::kGroups;
+  constexpr int kCache = kTileCache * G;
   extern __shared__ __align__(128) uint8_t smem[];
   __shared__ __align__(8) uint64_t full_bar[S];
-  __shared__ int done_cnt[S];                        // warps that have finished reading a stage
-  __shared__ int first_cnt[2];                       // arrivals at the last meeting of a tile, by tile parity
+  __shared__ int next_seq;                           // next tile of this CTA nobody has taken yet
+  __shared__ int claimed[G][2];                      // the tile a group goes on with, by parity of its tile count
+  __shared__ int first_cnt[G][2];                    // arrivals at the last meeting of a tile, by the same parity
   __shared__ int poison_flag;
-  __shared__ float head_red[2][kWarps];
-  __shared__ TileMeta meta_cache[kTileCache + kWarps];   // this CTA's first tiles; one spare entry per warp
-  __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? kWarps * kT : 4];   // per warp: q, scaled, as pairs
-  __shared__ __align__(16) float col_red[(LAYOUT == LAYOUT_KV) ? kWarps * kT * 4 : 4];
-  static_assert(sizeof(full_bar) + sizeof(done_cnt) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) +
-                        sizeof(q_warp) + sizeof(col_red) + 64 <= L::kStatic,
+  __shared__ float head_red[G][2][kWarps];
+  __shared__ TileMeta meta_cache[kCache + G * kWarps];   // this CTA's first tiles; one spare entry per warp
+  __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? G * kWarps * kT : 4];   // per warp: q, scaled, as pairs
+  __shared__ __align__(16) float col_red_all[(LAYOUT == LAYOUT_KV) ? G * kWarps * kT * 4 : 4];
+  static_assert(sizeof(full_bar) + sizeof(claimed) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) +
+                        sizeof(q_warp) + sizeof(col_red_all) + 64 <= L::kStatic,
                 "static shared memory exceeds what the stage ring was sized for");
+  static_assert(S >= 2 * G, "every group needs a stage in use and one on the way");
 
+  // warp: index within the whole CTA (per-warp scratch); gw, gtid: within the group (rows of the tile)
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = (G == 1) ? 0 : (warp >> 3), gw = warp & 7, gtid = tid & (kThreads - 1);
+  const int bar0 = 3 * grp;                          // this group's named barriers are bar0 + 1 .. bar0 + 3
+  float* col_red = col_red_all + ((LAYOUT == LAYOUT_KV) ? grp * kWarps * kT * 4 : 0);
 #ifdef CARRY_PROFILE
   const long long prof_k0 = clock64();
-  unsigned long long prof_g0;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(prof_g0));
 #endif
   const int total = p.B * p.HV;
   const int my_tiles = (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -516,27 +529,25 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 
   if (tid == 0) {
     poison_flag = 0;
-    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); done_cnt[s] = 0; }
-    first_cnt[0] = first_cnt[1] = 0;
+    next_seq = G;                                    // tiles 0 .. G-1 are the groups' first ones
+    for (int s = 0; s < S; ++s) mbar_init(&full_bar[s], 1);
+    for (int g = 0; g < G; ++g) first_cnt[g][0] = first_cnt[g][1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-#ifdef CARRY_PROFILE
-  const long long prof_p1 = clock64();
-#endif
-  // The first S tiles are requested before anything else: warp i fetches tile i's slot id (the only thing
-  // a request depends on) and issues that tile's copies.  Then all threads gather slot ids, gates and norms
-  // of this CTA's first tiles, four lanes per tile, in one trip to global memory.
-  if (lane == 0 && warp < S && warp < my_tiles) {
-    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
+  // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
+  // number % S.  The groups' first tiles are requested before anything else: a request depends on the
+  // tile's slot id alone.  Then all threads gather slot ids, gates and norms of the CTA's first tiles, four
+  // lanes per tile, in one trip to global memory; the rest of the ring is requested after that, so that
+  // the first tiles are not queued behind it.
+  auto issue_first = [&](int num) {
+    const int tile = (int)blockIdx.x + num * (int)gridDim.x;
     const int tn = tile / p.HV, thv = tile - tn * p.HV;
     const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, warp, tn, thv, tslot);
-  }
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, num, tn, thv, tslot);
+  };
+  if (lane == 0 && warp < G && warp < my_tiles) issue_first(warp);
   __syncwarp();
-#ifdef CARRY_PROFILE
-  const long long prof_p2 = clock64();
-#endif
   {
     static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
     const int i = tid >> 2;
@@ -544,33 +555,31 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     tile_meta4<QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid && (tid & 3) == 0,
                     &meta_cache[i]);
   }
-#ifdef CARRY_PROFILE
-  const long long prof_p3 = clock64();
-#endif
+  if (lane == 0 && warp >= G && warp < S && warp < my_tiles) issue_first(warp);
+  static_assert(S <= G * kWarps, "one warp per stage issues the first requests");
   __syncthreads();
-#ifdef CARRY_PROFILE
-  const long long prof_p4 = clock64();
-#endif
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
   const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
-  // Variants whose warps meet once per tile refill a stage one tile late: when tile `it` reaches its
-  // last meeting every warp has long left tile it-1, and the first warp to arrive -- the one with the
-  // most slack -- loads tile it-1+S into that stage while it waits for the others.  Variants without a
-  // meeting refill a stage as soon as its last reader is done with it.
-  constexpr bool kMeetRefill = (LAYOUT == LAYOUT_KV) || (RSCALE == CARRY_SCALE_PER_HEAD);
-  auto load_tile = [&](int nit) {
+  auto load_tile = [&](int num) {
     int tn, thv, tslot;
-    if (nit < kTileCache) { tn = meta_cache[nit].n; thv = meta_cache[nit].hv; tslot = meta_cache[nit].slot; }
-    else { const int tile = (int)blockIdx.x + nit * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
+    if (num < kCache) { tn = meta_cache[num].n; thv = meta_cache[num].hv; tslot = meta_cache[num].slot; }
+    else { const int tile = (int)blockIdx.x + num * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
            tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, nit % S, tn, thv, tslot);
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, num % S, tn, thv, tslot);
   };
-  auto refill_at_meeting = [&](int it) {          // called by lane 0 of every warp right before the last meeting
-    if (atomicAdd(&first_cnt[it & 1], 1) == 0) {
-      first_cnt[(it + 1) & 1] = 0;
-      if (it > 0 && it - 1 + S < my_tiles && !*poison) load_tile(it - 1 + S);
+  // A group takes its tiles from the CTA's list as it goes (the two groups of an SM do not run at the
+  // same pace).  Right before the last meeting of a tile, lane 0 of every warp calls claim_next(): the first
+  // to arrive takes the next number for the whole group.  Right after that meeting every read of the tile's
+  // stage is over, and one warp -- they take turns -- requests the tile that will use the stage next.
+  auto claim_next = [&](int cnt) {
+    if (atomicAdd(&first_cnt[grp][cnt & 1], 1) == 0) {
+      first_cnt[grp][(cnt + 1) & 1] = 0;
+      claimed[grp][cnt & 1] = atomicAdd(&next_seq, 1);
     }
+  };
+  auto refill_stage = [&](int cnt, int num) {
+    if (gw == (cnt & (kWarps - 1)) && lane == 0 && num + S < my_tiles && !*poison) load_tile(num + S);
   };
 
 #ifdef CARRY_PROFILE
@@ -580,13 +589,14 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #else
 #define PROF_MARK(k)
 #endif
-  for (int it = 0; it < my_tiles; ++it) {
+  int it = grp;                                      // number of the tile in hand
+  for (int cnt = 0; it < my_tiles; ++cnt) {
     const int s = it % S;
     const uint32_t parity = (uint32_t)(it / S) & 1u;
     uint8_t* sb = smem + (size_t)s * L::kBytes;
-    const TileMeta* tm = &meta_cache[it < kTileCache ? it : kTileCache + warp];
-    if (it >= kTileCache) {
-      tile_meta4<QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane == 0, &meta_cache[kTileCache + warp]);
+    const TileMeta* tm = &meta_cache[it < kCache ? it : kCache + warp];
+    if (it >= kCache) {
+      tile_meta4<QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane == 0, &meta_cache[kCache + warp]);
       __syncwarp();
     }
     const uint4 tm0 = lds_v4(tm);
@@ -605,9 +615,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     }
 
     if (!live) {
-      if (slot <= 0 && tid < kT) store_from_float(p.out, out_off + tid, p.o_dtype, 0.f);
-      if (LAYOUT == LAYOUT_KV) { warps_meet(1); warps_meet(2); }
-      if (kMeetRefill) { if (lane == 0) refill_at_meeting(it); warps_meet(3); }
+      if (slot <= 0 && gtid < kT) store_from_float(p.out, out_off + gtid, p.o_dtype, 0.f);
+      if (LAYOUT == LAYOUT_KV) { warps_meet(bar0 + 1); warps_meet(bar0 + 2); }
+      if (lane == 0) claim_next(cnt);
+      warps_meet(bar0 + 3);
+      refill_stage(cnt, it);
     } else {
       const uint4 tm1 = lds_v4(reinterpret_cast<const uint8_t*>(tm) + 16);
       const float alpha = __uint_as_float(tm0.w), beta = __uint_as_float(tm1.x), k_mul = __uint_as_float(tm1.y),
@@ -622,7 +634,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // lane: rows r0..r0+3, columns c0..c0+15.  A quad of columns (one 32-bit
         // word of codes) is held as two pairs: E = {col 0, col 2}, O = {col 1, col 3}.
         const int cg = lane & 7, rg = lane >> 3;
-        const int r0 = 16 * warp + 4 * rg, c0 = 16 * cg;
+        const int r0 = 16 * gw + 4 * rg, c0 = 16 * cg;
         float* qw = q_warp + warp * kT;
         {   // this warp's copy of q: fp32, scaled, each quad stored as {q0, q2, q1, q3}.  Quad j = 4 cg + m
             // sits at position 8 m + cg, so that the 8 lanes of a row group read 128 contiguous bytes.
@@ -728,19 +740,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         PROF_MARK(3)
         if (cg == 0) stg_v4(dst_sscale + r0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
                                                             __float_as_uint(snew[2]), __float_as_uint(snew[3])));
-        if constexpr (!kMeetRefill) {
-          // every read of this stage is done: the warp that sees that last refills it with tile it + S
-          __syncwarp();
-          if (lane == 0 && it + S < my_tiles) {
-            __threadfence_block();
-            if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
-              __threadfence_block();
-              done_cnt[s] = 0;
-              load_tile(it + S);
-            }
-          }
-        }
-
         // phase 3: state codes, new residual.  target - code * scale is one fused multiply-add, which is
         // exact here (the difference of two nearly equal numbers), so the target can be rebuilt from the
         // remainder when a row has to be re-decided.  No branch until all four rows are done.
@@ -791,6 +790,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // phase 4: residual scale and codes
         float esn[4], einv[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
+          if (lane == 0) claim_next(cnt);      // no data crosses warps here: the meeting only hands on the stage
+          warps_meet(bar0 + 3);
+          refill_stage(cnt, it);
+          PROF_MARK(5)
           const float s_mine = scale_fast(group_max4_transposed(eamax, cg), rqmax, rrqmax, p.eps_mode);
           const float i_mine = rcp_refined(s_mine);
 #pragma unroll
@@ -800,12 +803,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         } else {
           const float m4 = warp_max_nonneg(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
-          if (lane == 0) { head_red[it & 1][warp] = m4; refill_at_meeting(it); }
-          warps_meet(3);
+          if (lane == 0) { head_red[grp][cnt & 1][gw] = m4; claim_next(cnt); }
+          warps_meet(bar0 + 3);
+          refill_stage(cnt, it);
           PROF_MARK(5)
-          float m = head_red[it & 1][0];
+          float m = head_red[grp][cnt & 1][0];
 #pragma unroll
-          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
+          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[grp][cnt & 1][w]);
           const float e1 = scale_fast(m, rqmax, rrqmax, p.eps_mode);
           const float i1 = rcp_refined(e1);
 #pragma unroll
@@ -846,11 +850,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
           stg_v4(dst_rscale + r0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
                                                  __float_as_uint(esn[2]), __float_as_uint(esn[3])));
-        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
+        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
       } else {
         // ---------------- statequant layout [K][V]: lane = 4 columns x 16 rows ----
         // columns {c0, c0+1} are held as pair A, {c0+2, c0+3} as pair B
-        const int r0 = 16 * warp, c0 = 4 * lane;
+        const int r0 = 16 * gw, c0 = 4 * lane;
         float* red_dot = col_red;                       // [warp][col][2]
         float* red_max = col_red + kWarps * kT * 2;     // [warp][col]
         float* red_emax = red_max + kWarps * kT;        // [warp][col]
@@ -882,10 +886,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // finish the column sums across the 8 warps
         float dk[4], dq[4];
         {
-          float4* dst = reinterpret_cast<float4*>(red_dot + ((size_t)warp * kT + c0) * 2);
+          float4* dst = reinterpret_cast<float4*>(red_dot + ((size_t)gw * kT + c0) * 2);
           dst[0] = make_float4(dkA.x, dqA.x, dkA.y, dqA.y);
           dst[1] = make_float4(dkB.x, dqB.x, dkB.y, dqB.y);
-          warps_meet(1);
+          warps_meet(bar0 + 1);
 #pragma unroll
           for (int b = 0; b < 4; ++b) { dk[b] = 0.f; dq[b] = 0.f; }
 #pragma unroll
@@ -927,12 +931,12 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           amax[0] = fmaxf(amax[0], fabsf(tA.x)); amax[1] = fmaxf(amax[1], fabsf(tA.y));
           amax[2] = fmaxf(amax[2], fabsf(tB.x)); amax[3] = fmaxf(amax[3], fabsf(tB.y));
         }
-        if (warp == 0) {
+        if (gw == 0) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) store_from_float(p.out, out_off + c0 + b, p.o_dtype, oval[b]);
         }
-        *reinterpret_cast<float4*>(red_max + (size_t)warp * kT + c0) = make_float4(amax[0], amax[1], amax[2], amax[3]);
-        warps_meet(2);
+        *reinterpret_cast<float4*>(red_max + (size_t)gw * kT + c0) = make_float4(amax[0], amax[1], amax[2], amax[3]);
+        warps_meet(bar0 + 2);
 #pragma unroll
         for (int w = 0; w < kWarps; ++w) {
           const float4 x = *reinterpret_cast<const float4*>(red_max + (size_t)w * kT + c0);
@@ -973,10 +977,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         for (int i = 0; i < 16; ++i) stg_b32(dst_codes + (r0 + i) * kT + c0, cw[i]);
         float esn[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
-          *reinterpret_cast<float4*>(red_emax + (size_t)warp * kT + c0) =
+          *reinterpret_cast<float4*>(red_emax + (size_t)gw * kT + c0) =
               make_float4(eamax[0], eamax[1], eamax[2], eamax[3]);
-          if (lane == 0) refill_at_meeting(it);
-          warps_meet(3);
+          if (lane == 0) claim_next(cnt);
+          warps_meet(bar0 + 3);
+          refill_stage(cnt, it);
 #pragma unroll
           for (int w = 0; w < kWarps; ++w) {
             const float4 x = *reinterpret_cast<const float4*>(red_emax + (size_t)w * kT + c0);
@@ -987,11 +992,12 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           for (int b = 0; b < 4; ++b) esn[b] = scale_fast(eamax[b], rqmax, rrqmax, p.eps_mode);
         } else {
           float m = warp_max_nonneg(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
-          if (lane == 0) { head_red[it & 1][warp] = m; refill_at_meeting(it); }
-          warps_meet(3);
-          m = head_red[it & 1][0];
+          if (lane == 0) { head_red[grp][cnt & 1][gw] = m; claim_next(cnt); }
+          warps_meet(bar0 + 3);
+          refill_stage(cnt, it);
+          m = head_red[grp][cnt & 1][0];
 #pragma unroll
-          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[it & 1][w]);
+          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[grp][cnt & 1][w]);
           esn[0] = esn[1] = esn[2] = esn[3] = scale_fast(m, rqmax, rrqmax, p.eps_mode);
         }
         const float2 ieA = make_float2(rcp_refined(esn[0]), rcp_refined(esn[1]));
@@ -1010,55 +1016,28 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
         // scales: every warp holds all 128 of them; warp w publishes its 16-column share
         // (columns 16w..16w+15 are held by lanes 4w..4w+3)
-        if ((lane >> 2) == warp) {
+        if ((lane >> 2) == gw) {
           stg_v4(dst_sscale + c0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
                                                  __float_as_uint(snew[2]), __float_as_uint(snew[3])));
           if (RSCALE == CARRY_SCALE_PER_V)
             stg_v4(dst_rscale + c0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
                                                    __float_as_uint(esn[2]), __float_as_uint(esn[3])));
         }
-        if (RSCALE == CARRY_SCALE_PER_HEAD && tid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
+        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
       }
     }
     PROF_MARK(6)
 
-    // a skipped tile (padding slot) still has to hand its stage on
-    if (!kMeetRefill && !live && it + S < my_tiles) {
-      __syncwarp();
-      if (lane == 0) {
-        __threadfence_block();
-        if (atomicAdd(&done_cnt[s], 1) == kWarps - 1) {
-          __threadfence_block();
-          done_cnt[s] = 0;
-          if (healthy) load_tile(it + S);
-        }
-      }
-    }
-    PROF_MARK(10)
+    it = *reinterpret_cast<volatile int*>(&claimed[grp][cnt & 1]);   // written before this tile's last meeting
   }
 #ifdef CARRY_PROFILE
   if (lane == 0 && p.prof) {
-    for (int k = 0; k < 12; ++k) atomicAdd(reinterpret_cast<unsigned long long*>(p.prof) + k, (unsigned long long)prof_acc[k]);
-    unsigned long long g1;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g1));
     unsigned long long* pp = reinterpret_cast<unsigned long long*>(p.prof);
-    atomicMax(pp + 80, (unsigned long long)(clock64() - prof_k0));   // longest CTA, cycles
-    atomicMax(pp + 81, g1 - prof_g0);                                 // longest CTA, ns
-    atomicMin(pp + 82, prof_g0);                                      // first start
-    atomicMax(pp + 83, g1);                                           // last end
-    atomicAdd(pp + 84, (unsigned long long)(clock64() - prof_k0));   // sum over warps of kernel cycles
-    if (warp == 0) {
-      unsigned smid;
-      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-      pp[96 + 4 * blockIdx.x] = prof_g0;
-      pp[96 + 4 * blockIdx.x + 1] = g1;
-      pp[96 + 4 * blockIdx.x + 2] = smid;
-      pp[96 + 4 * blockIdx.x + 3] = (unsigned long long)prof_acc[0];
-    }
-    atomicAdd(pp + 85, (unsigned long long)(prof_p1 - prof_k0));
-    atomicAdd(pp + 86, (unsigned long long)(prof_p2 - prof_p1));
-    atomicAdd(pp + 87, (unsigned long long)(prof_p3 - prof_p2));
-    atomicAdd(pp + 88, (unsigned long long)(prof_p4 - prof_p3));
+    const unsigned long long cyc = (unsigned long long)(clock64() - prof_k0);
+    for (int k = 0; k < 12; ++k) atomicAdd(pp + k, (unsigned long long)prof_acc[k]);
+    atomicMax(pp + 80, cyc);                     // the warp that ran longest, cycles
+    atomicAdd(pp + 84, cyc);                     // all warps' cycles from kernel start to here
+    atomicMin(pp + 82, cyc);                     // the warp that was done first
   }
 #endif
   __syncthreads();
@@ -1080,9 +1059,10 @@ int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
     configured[dev] = true;
   }
   const long long tiles = (long long)p.B * p.HV;
-  const long long ctas = (long long)L::kCtasPerSm * sms;
-  const int grid = (int)(tiles < ctas ? tiles : ctas);
-  kern<<<grid, kThreads, smem, stream>>>(p);
+  const long long per_cta = L::kGroups;               // a CTA works on that many tiles at a time
+  const long long want = (tiles + per_cta - 1) / per_cta;
+  const int grid = (int)(want < sms ? want : sms);
+  kern<<<grid, kThreads * L::kGroups, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
 }
 
