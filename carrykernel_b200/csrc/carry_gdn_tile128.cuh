@@ -118,6 +118,23 @@ __device__ __forceinline__ uint4 lds_v4(const void* p) {
 __device__ __forceinline__ void stg_v4(unsigned long long addr, uint4 v) {
   asm volatile("st.global.v4.b32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
+// the same with a compile-time byte offset, so that one base register serves a run of stores
+template <int OFF>
+__device__ __forceinline__ void stg_v4_at(unsigned long long base, uint4 v) {
+  asm volatile("st.global.v4.b32 [%0+%5], {%1, %2, %3, %4};" ::"l"(base), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "n"(OFF)
+               : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ void stg_v2_at(unsigned long long base, uint2 v) {
+  asm volatile("st.global.v2.b32 [%0+%3], {%1, %2};" ::"l"(base), "r"(v.x), "r"(v.y), "n"(OFF) : "memory");
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds_f4_at(uint32_t base) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "r"(base), "n"(OFF));
+  return v;
+}
 __device__ __forceinline__ void stg_v2(unsigned long long addr, uint2 v) {
   asm volatile("st.global.v2.b32 [%0], {%1, %2};" ::"l"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
@@ -527,6 +544,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   const int my_tiles = (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   volatile int* poison = &poison_flag;
 
+  // let the next kernel in the stream, if it asked for it, move in behind this one (see launch_variant)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     poison_flag = 0;
     next_seq = G;                                    // tiles 0 .. G-1 are the groups' first ones
@@ -535,6 +554,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  // nothing before this line reads or writes global memory; everything after it sees the results of the
+  // kernels that precede this one in the stream
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
   // number % S.  The groups' first tiles are requested before anything else: a request depends on the
   // tile's slot id alone.  Then all threads gather slot ids, gates and norms of the CTA's first tiles, four
@@ -664,9 +686,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
               const float2 e = mul2(mul2(s8x2_to_float<0, 2>(w[m]), s2), alpha2);
               const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
               hE[i][m] = e; hO[i][m] = o;
-              float2 qe, qo;       // re-read per row on purpose: q must not stay in registers
-              asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                           : "=f"(qe.x), "=f"(qe.y), "=f"(qo.x), "=f"(qo.y) : "r"(q_addr + 128 * m));
+              // re-read per row on purpose: q must not stay in registers
+              const float4 qq = (m == 0) ? lds_f4_at<0>(q_addr) : (m == 1) ? lds_f4_at<128>(q_addr)
+                              : (m == 2) ? lds_f4_at<256>(q_addr) : lds_f4_at<384>(q_addr);
+              const float2 qe = make_float2(qq.x, qq.y), qo = make_float2(qq.z, qq.w);
               ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
               aq = fma2(e, qe, aq); aq = fma2(o, qo, aq);
             }
@@ -782,9 +805,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             }
           }
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i)
-          stg_v4(dst_codes + (r0 + i) * kT + c0, make_uint4(cw[i][0], cw[i][1], cw[i][2], cw[i][3]));
+        {
+          const unsigned long long base = dst_codes + r0 * kT + c0;
+          stg_v4_at<0 * kT>(base, make_uint4(cw[0][0], cw[0][1], cw[0][2], cw[0][3]));
+          stg_v4_at<1 * kT>(base, make_uint4(cw[1][0], cw[1][1], cw[1][2], cw[1][3]));
+          stg_v4_at<2 * kT>(base, make_uint4(cw[2][0], cw[2][1], cw[2][2], cw[2][3]));
+          stg_v4_at<3 * kT>(base, make_uint4(cw[3][0], cw[3][1], cw[3][2], cw[3][3]));
+        }
         PROF_MARK(4)
 
         // phase 4: residual scale and codes
@@ -834,7 +861,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             }
             const uint32_t w0 = pack4(by[0], by[1], by[2], by[3]) ^ 0x88888888u;
             const uint32_t w1 = pack4(by[4], by[5], by[6], by[7]) ^ 0x88888888u;
-            stg_v2(dst_resid + (r0 + i) * (kT / 2) + c0 / 2, make_uint2(w0, w1));
+            const unsigned long long base = dst_resid + r0 * (kT / 2) + c0 / 2;
+            if (i == 0) stg_v2_at<0 * (kT / 2)>(base, make_uint2(w0, w1));
+            if (i == 1) stg_v2_at<1 * (kT / 2)>(base, make_uint2(w0, w1));
+            if (i == 2) stg_v2_at<2 * (kT / 2)>(base, make_uint2(w0, w1));
+            if (i == 3) stg_v2_at<3 * (kT / 2)>(base, make_uint2(w0, w1));
           } else {
             uint32_t packed[4];
 #pragma unroll
@@ -844,7 +875,12 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
               packed[m] = pack4(__float_as_uint(ye.x), __float_as_uint(yo.x), __float_as_uint(ye.y),
                                 __float_as_uint(yo.y));
             }
-            stg_v4(dst_resid + (r0 + i) * kT + c0, make_uint4(packed[0], packed[1], packed[2], packed[3]));
+            const unsigned long long base = dst_resid + r0 * kT + c0;
+            const uint4 pw = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            if (i == 0) stg_v4_at<0 * kT>(base, pw);
+            if (i == 1) stg_v4_at<1 * kT>(base, pw);
+            if (i == 2) stg_v4_at<2 * kT>(base, pw);
+            if (i == 3) stg_v4_at<3 * kT>(base, pw);
           }
         }
         if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
@@ -1062,8 +1098,28 @@ int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
   const long long per_cta = L::kGroups;               // a CTA works on that many tiles at a time
   const long long want = (tiles + per_cta - 1) / per_cta;
   const int grid = (int)(want < sms ? want : sms);
-  kern<<<grid, kThreads * L::kGroups, smem, stream>>>(p);
-  return cudaGetLastError() == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
+  // Programmatic dependent launch: when the kernel before this one in the stream lets its dependents go
+  // early (this kernel does, at its top), the CTAs of this launch may take over SMs as that kernel's CTAs
+  // leave them and set up their barriers; they touch global memory only after griddepcontrol.wait, i.e.
+  // after the earlier kernel has completed and its writes are visible.  After any other kernel the
+  // attribute changes nothing.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3((unsigned)(kThreads * L::kGroups));
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+#ifdef CARRY_NO_PDL
+  cfg.numAttrs = 0;
+#else
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+#endif
+  const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p);
+  if (err != cudaSuccess) cudaGetLastError();
+  return err == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
 }
 
 template <int LAYOUT, int RES, int RSCALE>
