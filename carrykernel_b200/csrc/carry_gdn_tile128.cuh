@@ -121,19 +121,28 @@ __device__ __forceinline__ void stg_v4(unsigned long long addr, uint4 v) {
 // the same with a compile-time byte offset, so that one base register serves a run of stores
 template <int OFF>
 __device__ __forceinline__ void stg_v4_at(unsigned long long base, uint4 v) {
-  asm volatile("st.global.v4.b32 [%0+%5], {%1, %2, %3, %4};" ::"l"(base), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "n"(OFF)
-               : "memory");
+  asm volatile("st.global.v4.b32 [%0+%5], {%1, %2, %3, %4};" ::"l"(base), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w), "n"(OFF));
 }
 template <int OFF>
 __device__ __forceinline__ void stg_v2_at(unsigned long long base, uint2 v) {
-  asm volatile("st.global.v2.b32 [%0+%3], {%1, %2};" ::"l"(base), "r"(v.x), "r"(v.y), "n"(OFF) : "memory");
+  asm volatile("st.global.v2.b32 [%0+%3], {%1, %2};" ::"l"(base), "r"(v.x), "r"(v.y), "n"(OFF));
 }
-template <int OFF>
+// A shared-memory load the compiler may schedule freely (it is not volatile and claims no memory
+// effect) but may neither merge with the same load of another row (TAG differs) nor keep in registers
+// across rows.  Ordering against the stores that filled the location comes from `base`: it has to be
+// derived from order_token(), called after those stores and the barrier that publishes them.
+template <int OFF, int TAG>
 __device__ __forceinline__ float4 lds_f4_at(uint32_t base) {
   float4 v;
-  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-               : "r"(base), "n"(OFF));
+  asm("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];  // row %6" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+      : "r"(base), "n"(OFF), "n"(TAG));
   return v;
+}
+// a zero the compiler cannot see through, defined at this point of the program
+__device__ __forceinline__ uint32_t order_token() {
+  uint32_t t;
+  asm volatile("mov.u32 %0, 0;" : "=r"(t) : : "memory");
+  return t;
 }
 __device__ __forceinline__ void stg_v2(unsigned long long addr, uint2 v) {
   asm volatile("st.global.v2.b32 [%0], {%1, %2};" ::"l"(addr), "r"(v.x), "r"(v.y) : "memory");
@@ -380,7 +389,7 @@ __device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float&
 
 // What a CTA needs to know about one of its tiles before the data arrives.
 struct __align__(16) TileMeta {
-  int n, hv, slot;
+  int n, hv_h, slot;    // hv_h: value head in the low 16 bits, its key head above them
   float alpha, beta;
   float k_mul, q_mul;   // 1/|k| and scale/|q| (1 when the L2 norm is off or on the statequant path)
   float kq;             // <k, q> after those factors
@@ -397,14 +406,15 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
   constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
   TileMeta m;
   m.n = tile / p.HV;
-  m.hv = tile - m.n * p.HV;
+  const int hv = tile - m.n * p.HV;
+  const int h = p.packed ? hv / (p.HV / p.H) : hv;
+  m.hv_h = hv | (h << 16);
   long long q_off, k_off;
   if (p.packed) {
-    const int h = m.hv / (p.HV / p.H);
     q_off = (long long)m.n * p.stride_mixed_tok + (long long)h * kT;
     k_off = q_off + (long long)p.H * kT;
   } else {
-    q_off = k_off = ((long long)m.n * p.HV + m.hv) * kT;
+    q_off = k_off = ((long long)m.n * p.HV + hv) * kT;
   }
   const uint4* qp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + (q_off + 32 * sub) * qes);
   const uint4* kp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k) + (k_off + 32 * sub) * qes);
@@ -412,7 +422,7 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) { qv[j] = __ldg(qp + j); kv[j] = __ldg(kp + j); }
   m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
-  gates_of(p, m.n, m.hv, m.alpha, m.beta);
+  gates_of(p, m.n, hv, m.alpha, m.beta);
   float ks = 0.f, qs = 0.f, kq = 0.f;
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
@@ -447,20 +457,21 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
   if (store) *dst = m;
 }
 
-// Load one tile into stage `stage` (called by one thread).
+// Request one tile into the stage at `sb` (called by one thread): the stage header (slot id, the four
+// destination pointers), the stage barrier's single arrival announcing the bytes to come, then the
+// seven bulk copies -- in that order: copies started before their bytes were announced cost 20 % of the
+// kernel's time when measured.  `h` is the key head of value head `hv`.  `slot` <= 0 marks a padding
+// request: nothing is copied.
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_t* full_bar, int stage, int n, int hv,
-                                        long long slot) {
+__device__ __noinline__ void issue_tile(const KParams& p, uint8_t* sb, uint64_t* bar, int n, int hv, int h, long long slot) {
   using L = StageLayout<RES, LAYOUT, QDT>;
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
-  uint8_t* sb = smem + (size_t)stage * L::kBytes;
   if (p.packed && slot >= p.num_slots) {
     if (p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
     slot = 0;
   }
   *reinterpret_cast<volatile int*>(sb + L::kHeader) = (int)slot;
-  uint64_t* bar = &full_bar[stage];
   if (slot <= 0) { mbar_arrive(bar); return; }
   unsigned long long* dst = reinterpret_cast<unsigned long long*>(sb + L::kHeader + 16);
   constexpr long long KV = kT * kT;
@@ -472,7 +483,6 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* smem, uint64_
     resid = reinterpret_cast<const uint8_t*>(p.resid_in) + slot * p.stride_resid_slot + (long long)hv * L::kResidBytes;
     sscale = p.sscale_in + slot * p.stride_sscale_slot + (long long)hv * kT;
     rscale = p.rscale_in + slot * p.stride_rscale_slot + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : 0);
-    const int h = hv / (p.HV / p.H);
     const uint8_t* row = reinterpret_cast<const uint8_t*>(p.q) + (long long)n * p.stride_mixed_tok * qes;
     q = row + (long long)h * kT * qes;
     k = row + ((long long)p.H * kT + (long long)h * kT) * qes;
@@ -565,11 +575,15 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   auto issue_first = [&](int num) {
     const int tile = (int)blockIdx.x + num * (int)gridDim.x;
     const int tn = tile / p.HV, thv = tile - tn * p.HV;
+    const int th = p.packed ? thv / (p.HV / p.H) : thv;
     const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, num, tn, thv, tslot);
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], tn, thv, th, tslot);
   };
   if (lane == 0 && warp < G && warp < my_tiles) issue_first(warp);
   __syncwarp();
+#ifdef CARRY_PROFILE
+  const long long prof_p2 = clock64();
+#endif
   {
     static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
     const int i = tid >> 2;
@@ -577,23 +591,37 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     tile_meta4<QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid && (tid & 3) == 0,
                     &meta_cache[i]);
   }
+#ifdef CARRY_PROFILE
+  const long long prof_p3 = clock64();
+#endif
   if (lane == 0 && warp >= G && warp < S && warp < my_tiles) issue_first(warp);
   static_assert(S <= G * kWarps, "one warp per stage issues the first requests");
   __syncthreads();
+#ifdef CARRY_PROFILE
+  const long long prof_p4 = clock64();
+#endif
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
   const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
-  auto load_tile = [&](int num) {
-    int tn, thv, tslot;
-    if (num < kCache) { tn = meta_cache[num].n; thv = meta_cache[num].hv; tslot = meta_cache[num].slot; }
-    else { const int tile = (int)blockIdx.x + num * (int)gridDim.x; tn = tile / p.HV; thv = tile - tn * p.HV;
-           tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1; }
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem, full_bar, num % S, tn, thv, tslot);
+  auto load_tile = [&](int num) {                   // one thread requests tile `num`
+    int tn, thv, th, tslot;
+    if (num < kCache) {
+      const uint4 m0 = lds_v4(&meta_cache[num]);
+      tn = (int)m0.x; thv = (int)(m0.y & 0xffffu); th = (int)(m0.y >> 16); tslot = (int)m0.z;
+    } else {
+      const int tile = (int)blockIdx.x + num * (int)gridDim.x;
+      tn = tile / p.HV; thv = tile - tn * p.HV;
+      th = p.packed ? thv / (p.HV / p.H) : thv;
+      tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
+    }
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)(num % S) * L::kBytes, &full_bar[num % S], tn, thv, th, tslot);
   };
   // A group takes its tiles from the CTA's list as it goes (the two groups of an SM do not run at the
   // same pace).  Right before the last meeting of a tile, lane 0 of every warp calls claim_next(): the first
   // to arrive takes the next number for the whole group.  Right after that meeting every read of the tile's
-  // stage is over, and one warp -- they take turns -- requests the tile that will use the stage next.
+  // stage is over, and one warp -- they take turns -- requests the tile that will use the stage next while
+  // the others go on.  (Measured alternatives, both slower: the first warp to arrive requesting, before the
+  // meeting, the tile for the stage of the group's previous tile; all eight warps requesting a part each.)
   auto claim_next = [&](int cnt) {
     if (atomicAdd(&first_cnt[grp][cnt & 1], 1) == 0) {
       first_cnt[grp][(cnt + 1) & 1] = 0;
@@ -622,7 +650,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       __syncwarp();
     }
     const uint4 tm0 = lds_v4(tm);
-    const int n = (int)tm0.x, hv = (int)tm0.y;
+    const int n = (int)tm0.x, hv = (int)(tm0.y & 0xffffu);
 
     const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
     PROF_MARK(0)
@@ -667,6 +695,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         float2 kE[4], kO[4];
         act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
         __syncwarp();
+        const uint32_t q_token = order_token();
 
         float2 hE[4][4], hO[4][4];       // [row][quad]
         float dk[4], dq[4];
@@ -674,7 +703,14 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         {
           const float4 s4 = *reinterpret_cast<const float4*>(sscale + r0);
           const float srow[4] = {s4.x, s4.y, s4.z, s4.w};
-          const uint32_t q_addr = smem_u32(qw + 4 * cg);
+          const uint32_t q_addr = smem_u32(qw + 4 * cg) + q_token;
+          auto q_quad = [&](int row, int m) -> float4 {
+#define CARRY_Q_ROW(R)                                                                                    \
+  ((m == 0) ? lds_f4_at<0, R>(q_addr) : (m == 1) ? lds_f4_at<128, R>(q_addr)                              \
+                                      : (m == 2) ? lds_f4_at<256, R>(q_addr) : lds_f4_at<384, R>(q_addr))
+            return (row == 0) ? CARRY_Q_ROW(0) : (row == 1) ? CARRY_Q_ROW(1) : (row == 2) ? CARRY_Q_ROW(2) : CARRY_Q_ROW(3);
+#undef CARRY_Q_ROW
+          };
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
@@ -687,8 +723,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
               const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
               hE[i][m] = e; hO[i][m] = o;
               // re-read per row on purpose: q must not stay in registers
-              const float4 qq = (m == 0) ? lds_f4_at<0>(q_addr) : (m == 1) ? lds_f4_at<128>(q_addr)
-                              : (m == 2) ? lds_f4_at<256>(q_addr) : lds_f4_at<384>(q_addr);
+              const float4 qq = q_quad(i, m);
               const float2 qe = make_float2(qq.x, qq.y), qo = make_float2(qq.z, qq.w);
               ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
               aq = fma2(e, qe, aq); aq = fma2(o, qo, aq);
@@ -1074,6 +1109,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     atomicMax(pp + 80, cyc);                     // the warp that ran longest, cycles
     atomicAdd(pp + 84, cyc);                     // all warps' cycles from kernel start to here
     atomicMin(pp + 82, cyc);                     // the warp that was done first
+    atomicAdd(pp + 85, (unsigned long long)(prof_p1 - prof_k0));
+    atomicAdd(pp + 86, (unsigned long long)(prof_p2 - prof_p1));
+    atomicAdd(pp + 87, (unsigned long long)(prof_p3 - prof_p2));
+    atomicAdd(pp + 88, (unsigned long long)(prof_p4 - prof_p3));
   }
 #endif
   __syncthreads();
