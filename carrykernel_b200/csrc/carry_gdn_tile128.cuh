@@ -273,8 +273,8 @@ __device__ __forceinline__ float warp_sum32(float x) {
 // Static shared memory next to the stage ring: barriers, the per-CTA tile caches,
 // the per-warp q scratch (slot layout) or the column-reduction space (statequant
 // layout).  Upper bounds, used to size the ring.
-constexpr int kStaticVK = 7168;         // per group
-constexpr int kStaticKV = 19456;
+constexpr int kStaticVK = 11776;        // per group
+constexpr int kStaticKV = 24064;
 constexpr int kStaticOf(int layout) { return layout == 0 ? kStaticVK : kStaticKV; }
 constexpr int kSmemPerCta = 231424;     // one CTA per SM: 227 KB less 1 KB
 
@@ -289,8 +289,8 @@ struct StageLayout {
   static constexpr int kQ = kRScale + 512;                   // raw q, k, v of this head
   static constexpr int kK = kQ + kVecBytes;
   static constexpr int kV = kK + kVecBytes;
-  static constexpr int kHeader = kV + kVecBytes;             // int slot, then the 4 destination pointers
-  static constexpr int kBytes = kHeader + 48;
+  static constexpr int kBytes = kV + kVecBytes;
+  static_assert(kBytes % 128 == 0, "stages keep the ring's 128-byte alignment");
   // Two groups of 8 warps share one CTA (and one SM) when a group's registers allow it -- at least 3
   // stages per group must fit too -- else the CTA is a single group.
 #ifdef CARRY_FORCE_1GROUP
@@ -396,12 +396,53 @@ struct __align__(16) TileMeta {
 };
 static_assert(sizeof(TileMeta) == 32, "TileMeta is read as two 16-byte words");
 
+// Where a tile's data lives: the four places its results go (codes, residual, state scales, residual
+// scale(s)), then the sources that are not one of those (residual scales as read, q, k, v).  Codes,
+// residual and state scales are read from the destination plus the launch-wide offset between the input
+// and the output arrays (zero on the slot path, which works in place).
+struct __align__(16) TileDesc {
+  unsigned long long a[8];
+};
+enum { D_CODES = 0, D_RESID = 1, D_SSCALE = 2, D_RSCALE = 3, D_RSCALE_IN = 4, D_Q = 5, D_K = 6, D_V = 7 };
+
+template <int RES, int RSCALE, int QDT>
+__device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, int h, long long slot,
+                                               unsigned long long (&a)[8]) {
+  constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
+  constexpr long long KV = kT * kT;
+  constexpr long long RB = (RES == CARRY_RES_INT4) ? KV / 2 : KV;
+  const long long nh = (long long)n * p.HV + hv;
+  if (p.packed) {
+    a[D_CODES] = reinterpret_cast<unsigned long long>(p.codes_out + slot * p.stride_state_slot + hv * KV);
+    a[D_RESID] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(p.resid_out) + slot * p.stride_resid_slot + hv * RB);
+    a[D_SSCALE] = reinterpret_cast<unsigned long long>(p.sscale_out + slot * p.stride_sscale_slot + (long long)hv * kT);
+    const float* rs = p.rscale_out + slot * p.stride_rscale_slot;
+    a[D_RSCALE] = reinterpret_cast<unsigned long long>(rs + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : (long long)hv));
+    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(rs + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : 0));
+    const uint8_t* row = reinterpret_cast<const uint8_t*>(p.q) + (long long)n * p.stride_mixed_tok * qes;
+    a[D_Q] = reinterpret_cast<unsigned long long>(row + (long long)h * kT * qes);
+    a[D_K] = reinterpret_cast<unsigned long long>(row + ((long long)p.H + h) * kT * qes);
+    a[D_V] = reinterpret_cast<unsigned long long>(row + (2LL * p.H + hv) * kT * qes);
+  } else {
+    a[D_CODES] = reinterpret_cast<unsigned long long>(p.codes_out + nh * KV);
+    a[D_RESID] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(p.resid_out) + nh * RB);
+    a[D_SSCALE] = reinterpret_cast<unsigned long long>(p.sscale_out + nh * kT);
+    a[D_RSCALE] = reinterpret_cast<unsigned long long>(p.rscale_out + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : nh));
+    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(p.rscale_in + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : (long long)n * p.HV));
+    a[D_Q] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.q) + nh * kT * qes);
+    a[D_K] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes);
+    a[D_V] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes);
+  }
+}
+
 // Computed by four consecutive lanes straight from global memory: slot id, gates, and the norms of k
 // and q (32 elements per lane, then a sum over the four lanes).  Every load depends on the tile index
 // alone, so the whole thing is one trip to memory however many tiles a CTA prepares at once.  All 32
-// lanes of a warp must call this together; the first lane of a group writes `dst` when `store` is set.
-template <int QDT>
-__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst) {
+// lanes of a warp must call this together; when `store` is set the first lane of a group writes `dst`
+// and each of the four lanes a quarter of the tile's addresses to `ddst`.  A slot id beyond the pool is
+// reported in the status word and treated as padding.
+template <int RES, int RSCALE, int QDT>
+__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst) {
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
   TileMeta m;
@@ -454,67 +495,59 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
     m.q_mul *= p.qscale;
   }
   m.kq = kq * (m.k_mul * m.q_mul);
-  if (store) *dst = m;
+  if (p.packed && m.slot >= p.num_slots) {
+    if (store && sub == 0 && p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
+    m.slot = 0;
+  }
+  if (store) {
+    if (sub == 0) *dst = m;
+    unsigned long long a[8];
+    tile_addresses<RES, RSCALE, QDT>(p, m.n, hv, h, m.slot > 0 ? m.slot : 0, a);
+    const unsigned long long lo = (sub == 0) ? a[0] : (sub == 1) ? a[2] : (sub == 2) ? a[4] : a[6];
+    const unsigned long long hi = (sub == 0) ? a[1] : (sub == 1) ? a[3] : (sub == 2) ? a[5] : a[7];
+    *reinterpret_cast<ulonglong2*>(&ddst->a[2 * sub]) = make_ulonglong2(lo, hi);
+  }
 }
 
-// Request one tile into the stage at `sb` (called by one thread): the stage header (slot id, the four
-// destination pointers), the stage barrier's single arrival announcing the bytes to come, then the
-// seven bulk copies -- in that order: copies started before their bytes were announced cost 20 % of the
-// kernel's time when measured.  `h` is the key head of value head `hv`.  `slot` <= 0 marks a padding
-// request: nothing is copied.
+// Request one tile into the stage at `sb` (called by one thread): the stage barrier's single arrival
+// announcing the bytes to come, then the seven bulk copies -- in that order: copies started before their
+// bytes were announced cost 20 % of the kernel's time when measured.  `slot` <= 0 marks a padding request:
+// nothing is copied.
+template <int LAYOUT, int RES, int RSCALE, int QDT>
+__device__ __forceinline__ void issue_copies(const KParams& p, uint8_t* sb, uint64_t* bar, const unsigned long long (&a)[8]) {
+  using L = StageLayout<RES, LAYOUT, QDT>;
+  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
+  // launch-wide offsets from where results go to where the state is read (zero when in place)
+  const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
+  const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
+  const long long d_sscale = reinterpret_cast<const uint8_t*>(p.sscale_in) - reinterpret_cast<const uint8_t*>(p.sscale_out);
+  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes);
+  bulk_load(sb + L::kCodes, reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT, bar);
+  bulk_load(sb + L::kResid, reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes, bar);
+  bulk_load(sb + L::kSScale, reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512, bar);
+  bulk_load(sb + L::kRScale, reinterpret_cast<const void*>(a[D_RSCALE_IN]), rscale_bytes, bar);
+  bulk_load(sb + L::kQ, reinterpret_cast<const void*>(a[D_Q]), L::kVecBytes, bar);
+  bulk_load(sb + L::kK, reinterpret_cast<const void*>(a[D_K]), L::kVecBytes, bar);
+  bulk_load(sb + L::kV, reinterpret_cast<const void*>(a[D_V]), L::kVecBytes, bar);
+}
+// ... from the tile's facts (the CTA's first requests, and tiles beyond the cached ones)
 template <int LAYOUT, int RES, int RSCALE, int QDT>
 __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* sb, uint64_t* bar, int n, int hv, int h, long long slot) {
-  using L = StageLayout<RES, LAYOUT, QDT>;
-  constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
-  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
-  if (p.packed && slot >= p.num_slots) {
-    if (p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
-    slot = 0;
-  }
-  *reinterpret_cast<volatile int*>(sb + L::kHeader) = (int)slot;
+  if (slot <= 0 || (p.packed && slot >= p.num_slots)) { mbar_arrive(bar); return; }
+  unsigned long long a[8];
+  tile_addresses<RES, RSCALE, QDT>(p, n, hv, h, slot, a);
+  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a);
+}
+// ... from the addresses worked out when the CTA started
+template <int LAYOUT, int RES, int RSCALE, int QDT>
+__device__ __noinline__ void issue_cached(const KParams& p, uint8_t* sb, uint64_t* bar, const TileDesc* d, int slot) {
   if (slot <= 0) { mbar_arrive(bar); return; }
-  unsigned long long* dst = reinterpret_cast<unsigned long long*>(sb + L::kHeader + 16);
-  constexpr long long KV = kT * kT;
-  const int8_t* codes;
-  const uint8_t *resid, *q, *k, *v;
-  const float *sscale, *rscale;
-  if (p.packed) {
-    codes = p.codes_in + slot * p.stride_state_slot + hv * KV;
-    resid = reinterpret_cast<const uint8_t*>(p.resid_in) + slot * p.stride_resid_slot + (long long)hv * L::kResidBytes;
-    sscale = p.sscale_in + slot * p.stride_sscale_slot + (long long)hv * kT;
-    rscale = p.rscale_in + slot * p.stride_rscale_slot + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : 0);
-    const uint8_t* row = reinterpret_cast<const uint8_t*>(p.q) + (long long)n * p.stride_mixed_tok * qes;
-    q = row + (long long)h * kT * qes;
-    k = row + ((long long)p.H * kT + (long long)h * kT) * qes;
-    v = row + (2LL * p.H * kT + (long long)hv * kT) * qes;
-    // in place: the results go back where the tile came from
-    dst[0] = reinterpret_cast<unsigned long long>(codes);
-    dst[1] = reinterpret_cast<unsigned long long>(resid);
-    dst[2] = reinterpret_cast<unsigned long long>(sscale);
-    dst[3] = reinterpret_cast<unsigned long long>(p.rscale_out + slot * p.stride_rscale_slot +
-                                                  (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : (long long)hv));
-  } else {
-    const long long nh = (long long)n * p.HV + hv;
-    codes = p.codes_in + nh * KV;
-    resid = reinterpret_cast<const uint8_t*>(p.resid_in) + nh * L::kResidBytes;
-    sscale = p.sscale_in + nh * kT;
-    rscale = p.rscale_in + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : (long long)n * p.HV);
-    q = reinterpret_cast<const uint8_t*>(p.q) + nh * kT * qes;
-    k = reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes;
-    v = reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes;
-    dst[0] = reinterpret_cast<unsigned long long>(p.codes_out + nh * KV);
-    dst[1] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(p.resid_out) + nh * L::kResidBytes);
-    dst[2] = reinterpret_cast<unsigned long long>(p.sscale_out + nh * kT);
-    dst[3] = reinterpret_cast<unsigned long long>(p.rscale_out + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : nh));
-  }
-  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes);
-  bulk_load(sb + L::kCodes, codes, kT * kT, bar);
-  bulk_load(sb + L::kResid, resid, L::kResidBytes, bar);
-  bulk_load(sb + L::kSScale, sscale, 512, bar);
-  bulk_load(sb + L::kRScale, rscale, rscale_bytes, bar);
-  bulk_load(sb + L::kQ, q, L::kVecBytes, bar);
-  bulk_load(sb + L::kK, k, L::kVecBytes, bar);
-  bulk_load(sb + L::kV, v, L::kVecBytes, bar);
+  const uint4 w0 = lds_v4(d), w1 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 16);
+  const uint4 w2 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 32), w3 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 48);
+  auto u64 = [](uint32_t lo, uint32_t hi) { return ((unsigned long long)hi << 32) | lo; };
+  const unsigned long long a[8] = {u64(w0.x, w0.y), u64(w0.z, w0.w), u64(w1.x, w1.y), u64(w1.z, w1.w),
+                                   u64(w2.x, w2.y), u64(w2.z, w2.w), u64(w3.x, w3.y), u64(w3.z, w3.w)};
+  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a);
 }
 
 // ---------------------------------------------------------------------------
@@ -535,9 +568,10 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   __shared__ int poison_flag;
   __shared__ float head_red[G][2][kWarps];
   __shared__ TileMeta meta_cache[kCache + G * kWarps];   // this CTA's first tiles; one spare entry per warp
+  __shared__ TileDesc desc_cache[kCache + G * kWarps];   // their addresses
   __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? G * kWarps * kT : 4];   // per warp: q, scaled, as pairs
   __shared__ __align__(16) float col_red_all[(LAYOUT == LAYOUT_KV) ? G * kWarps * kT * 4 : 4];
-  static_assert(sizeof(full_bar) + sizeof(claimed) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) +
+  static_assert(sizeof(full_bar) + sizeof(claimed) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) + sizeof(desc_cache) +
                         sizeof(q_warp) + sizeof(col_red_all) + 64 <= L::kStatic,
                 "static shared memory exceeds what the stage ring was sized for");
   static_assert(S >= 2 * G, "every group needs a stage in use and one on the way");
@@ -588,8 +622,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
     const int i = tid >> 2;
     const bool valid = i < my_tiles;
-    tile_meta4<QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid && (tid & 3) == 0,
-                    &meta_cache[i]);
+    tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
+                                 &meta_cache[i], &desc_cache[i]);
   }
 #ifdef CARRY_PROFILE
   const long long prof_p3 = clock64();
@@ -604,17 +638,16 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
   const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
   auto load_tile = [&](int num) {                   // one thread requests tile `num`
-    int tn, thv, th, tslot;
+    uint8_t* dst_stage = smem + (size_t)(num % S) * L::kBytes;
     if (num < kCache) {
-      const uint4 m0 = lds_v4(&meta_cache[num]);
-      tn = (int)m0.x; thv = (int)(m0.y & 0xffffu); th = (int)(m0.y >> 16); tslot = (int)m0.z;
+      issue_cached<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], &desc_cache[num], meta_cache[num].slot);
     } else {
       const int tile = (int)blockIdx.x + num * (int)gridDim.x;
-      tn = tile / p.HV; thv = tile - tn * p.HV;
-      th = p.packed ? thv / (p.HV / p.H) : thv;
-      tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
+      const int tn = tile / p.HV, thv = tile - tn * p.HV;
+      const int th = p.packed ? thv / (p.HV / p.H) : thv;
+      const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
+      issue_tile<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], tn, thv, th, tslot);
     }
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)(num % S) * L::kBytes, &full_bar[num % S], tn, thv, th, tslot);
   };
   // A group takes its tiles from the CTA's list as it goes (the two groups of an SM do not run at the
   // same pace).  Right before the last meeting of a tile, lane 0 of every warp calls claim_next(): the first
@@ -629,6 +662,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     }
   };
   auto refill_stage = [&](int cnt, int num) {
+#ifdef CARRY_EXP_NOREFILL
+    return;
+#endif
     if (gw == (cnt & (kWarps - 1)) && lane == 0 && num + S < my_tiles && !*poison) load_tile(num + S);
   };
 
@@ -644,22 +680,28 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const int s = it % S;
     const uint32_t parity = (uint32_t)(it / S) & 1u;
     uint8_t* sb = smem + (size_t)s * L::kBytes;
-    const TileMeta* tm = &meta_cache[it < kCache ? it : kCache + warp];
+    const int entry = it < kCache ? it : kCache + warp;
+    const TileMeta* tm = &meta_cache[entry];
     if (it >= kCache) {
-      tile_meta4<QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane == 0, &meta_cache[kCache + warp]);
+      tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane < 4, &meta_cache[entry],
+                                   &desc_cache[entry]);
       __syncwarp();
     }
     const uint4 tm0 = lds_v4(tm);
     const int n = (int)tm0.x, hv = (int)(tm0.y & 0xffffu);
 
+#ifdef CARRY_EXP_NOREFILL
+    const bool healthy = (it >= S) ? true : mbar_wait(&full_bar[s], parity, poison, p.status);
+#else
     const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
+#endif
     PROF_MARK(0)
-    const int slot = lds_i32(sb + L::kHeader);
+    const int slot = (int)tm0.z;
     const long long out_off = ((long long)n * p.HV + hv) * kT;
     const bool live = slot > 0 && healthy;
     unsigned long long dst_codes = 0, dst_resid = 0, dst_sscale = 0, dst_rscale = 0;
     if (live) {
-      const uint4 d0 = lds_v4(sb + L::kHeader + 16), d1 = lds_v4(sb + L::kHeader + 32);
+      const uint4 d0 = lds_v4(&desc_cache[entry]), d1 = lds_v4(reinterpret_cast<const uint8_t*>(&desc_cache[entry]) + 16);
       dst_codes = ((unsigned long long)d0.y << 32) | d0.x; dst_resid = ((unsigned long long)d0.w << 32) | d0.z;
       dst_sscale = ((unsigned long long)d1.y << 32) | d1.x; dst_rscale = ((unsigned long long)d1.w << 32) | d1.z;
     }
