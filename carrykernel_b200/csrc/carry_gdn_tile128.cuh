@@ -603,17 +603,20 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
   // number % S.  The groups' first tiles are requested before anything else: a request depends on the
-  // tile's slot id alone.  Then all threads gather slot ids, gates and norms of the CTA's first tiles, four
-  // lanes per tile, in one trip to global memory; the rest of the ring is requested after that, so that
-  // the first tiles are not queued behind it.
-  auto issue_first = [&](int num) {
-    const int tile = (int)blockIdx.x + num * (int)gridDim.x;
+  // tile's slot id alone.  Then all threads gather slot ids, gates, norms and addresses of the CTA's first
+  // tiles, four lanes per tile, in one trip to global memory; the rest of the ring is requested after
+  // that, so that the first tiles are not queued behind it.  (Gathering first and requesting the whole
+  // ring afterwards was measured 3 us slower per launch.)
+#ifdef CARRY_PROFILE
+  const long long prof_p1 = clock64();
+#endif
+  if (lane == 0 && warp < G && warp < my_tiles) {
+    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
     const int tn = tile / p.HV, thv = tile - tn * p.HV;
     const int th = p.packed ? thv / (p.HV / p.H) : thv;
     const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], tn, thv, th, tslot);
-  };
-  if (lane == 0 && warp < G && warp < my_tiles) issue_first(warp);
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)warp * L::kBytes, &full_bar[warp], tn, thv, th, tslot);
+  }
   __syncwarp();
 #ifdef CARRY_PROFILE
   const long long prof_p2 = clock64();
@@ -628,9 +631,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #ifdef CARRY_PROFILE
   const long long prof_p3 = clock64();
 #endif
-  if (lane == 0 && warp >= G && warp < S && warp < my_tiles) issue_first(warp);
-  static_assert(S <= G * kWarps, "one warp per stage issues the first requests");
   __syncthreads();
+  static_assert(S <= G * kWarps && S <= kTileCache, "one warp per stage issues the first requests, from the cache");
 #ifdef CARRY_PROFILE
   const long long prof_p4 = clock64();
 #endif
@@ -649,6 +651,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       issue_tile<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], tn, thv, th, tslot);
     }
   };
+  if (lane == 0 && warp >= G && warp < S && warp < my_tiles) load_tile(warp);
+  __syncwarp();
   // A group takes its tiles from the CTA's list as it goes (the two groups of an SM do not run at the
   // same pace).  Right before the last meeting of a tile, lane 0 of every warp calls claim_next(): the first
   // to arrive takes the next number for the whole group.  Right after that meeting every read of the tile's
@@ -697,17 +701,17 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #endif
     PROF_MARK(0)
     const int slot = (int)tm0.z;
-    const long long out_off = ((long long)n * p.HV + hv) * kT;
+    const int out_row = n * p.HV + hv;                // outputs of this tile start at element out_row * 128
     const bool live = slot > 0 && healthy;
-    unsigned long long dst_codes = 0, dst_resid = 0, dst_sscale = 0, dst_rscale = 0;
-    if (live) {
-      const uint4 d0 = lds_v4(&desc_cache[entry]), d1 = lds_v4(reinterpret_cast<const uint8_t*>(&desc_cache[entry]) + 16);
-      dst_codes = ((unsigned long long)d0.y << 32) | d0.x; dst_resid = ((unsigned long long)d0.w << 32) | d0.z;
-      dst_sscale = ((unsigned long long)d1.y << 32) | d1.x; dst_rscale = ((unsigned long long)d1.w << 32) | d1.z;
-    }
+    // where results go: read from the tile's cached addresses right before each use, not held in registers
+    auto dst_of = [&](int which) -> unsigned long long {
+      unsigned long long v;
+      asm volatile("ld.shared.b64 %0, [%1];" : "=l"(v) : "r"(smem_u32(&desc_cache[entry].a[which])));
+      return v;
+    };
 
     if (!live) {
-      if (slot <= 0 && gtid < kT) store_from_float(p.out, out_off + gtid, p.o_dtype, 0.f);
+      if (slot <= 0 && gtid < kT) store_from_float(p.out, (long long)out_row * kT + gtid, p.o_dtype, 0.f);
       if (LAYOUT == LAYOUT_KV) { warps_meet(bar0 + 1); warps_meet(bar0 + 2); }
       if (lane == 0) claim_next(cnt);
       warps_meet(bar0 + 3);
@@ -790,7 +794,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           if (cg >= 4) {                      // the lanes that hold a q total finish that row's output
             const int i = cg & 3;
             const float dv_i = (i == 0) ? dvr[0] : (i == 1) ? dvr[1] : (i == 2) ? dvr[2] : dvr[3];
-            store_from_float(p.out, out_off + r0 + i, p.o_dtype, fmaf(dv_i, kq, dot_mine));
+            store_from_float(p.out, (long long)out_row * kT + r0 + i, p.o_dtype, fmaf(dv_i, kq, dot_mine));
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -838,7 +842,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
         PROF_MARK(3)
-        if (cg == 0) stg_v4(dst_sscale + r0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
+        if (cg == 0) stg_v4(dst_of(D_SSCALE) + r0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
                                                             __float_as_uint(snew[2]), __float_as_uint(snew[3])));
         // phase 3: state codes, new residual.  target - code * scale is one fused multiply-add, which is
         // exact here (the difference of two nearly equal numbers), so the target can be rebuilt from the
@@ -883,7 +887,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
         {
-          const unsigned long long base = dst_codes + r0 * kT + c0;
+          const unsigned long long base = dst_of(D_CODES) + r0 * kT + c0;
           stg_v4_at<0 * kT>(base, make_uint4(cw[0][0], cw[0][1], cw[0][2], cw[0][3]));
           stg_v4_at<1 * kT>(base, make_uint4(cw[1][0], cw[1][1], cw[1][2], cw[1][3]));
           stg_v4_at<2 * kT>(base, make_uint4(cw[2][0], cw[2][1], cw[2][2], cw[2][3]));
@@ -919,6 +923,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #pragma unroll
           for (int i = 0; i < 4; ++i) { esn[i] = e1; einv[i] = i1; }
         }
+        const unsigned long long dst_resid = dst_of(D_RESID);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float2 invE = splat(einv[i]);
@@ -961,9 +966,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           }
         }
         if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
-          stg_v4(dst_rscale + r0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
+          stg_v4(dst_of(D_RSCALE) + r0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
                                                  __float_as_uint(esn[2]), __float_as_uint(esn[3])));
-        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
+        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_of(D_RSCALE), __float_as_uint(esn[0]));
       } else {
         // ---------------- statequant layout [K][V]: lane = 4 columns x 16 rows ----
         // columns {c0, c0+1} are held as pair A, {c0+2, c0+3} as pair B
@@ -1046,7 +1051,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
         if (gw == 0) {
 #pragma unroll
-          for (int b = 0; b < 4; ++b) store_from_float(p.out, out_off + c0 + b, p.o_dtype, oval[b]);
+          for (int b = 0; b < 4; ++b) store_from_float(p.out, (long long)out_row * kT + c0 + b, p.o_dtype, oval[b]);
         }
         *reinterpret_cast<float4*>(red_max + (size_t)gw * kT + c0) = make_float4(amax[0], amax[1], amax[2], amax[3]);
         warps_meet(bar0 + 2);
@@ -1086,8 +1091,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             eamax[2] = fmaxf(eamax[2], fabsf(hB[i].x)); eamax[3] = fmaxf(eamax[3], fabsf(hB[i].y));
           }
         }
+        {
+          const unsigned long long dst_codes = dst_of(D_CODES);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) stg_b32(dst_codes + (r0 + i) * kT + c0, cw[i]);
+          for (int i = 0; i < 16; ++i) stg_b32(dst_codes + (r0 + i) * kT + c0, cw[i]);
+        }
         float esn[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
           *reinterpret_cast<float4*>(red_emax + (size_t)gw * kT + c0) =
@@ -1115,6 +1123,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
         const float2 ieA = make_float2(rcp_refined(esn[0]), rcp_refined(esn[1]));
         const float2 ieB = make_float2(rcp_refined(esn[2]), rcp_refined(esn[3]));
+        const unsigned long long dst_resid = dst_of(D_RESID);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           const float2 rA = fma2(hA[i], ieA, magic2), rB = fma2(hB[i], ieB, magic2);
@@ -1130,13 +1139,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         // scales: every warp holds all 128 of them; warp w publishes its 16-column share
         // (columns 16w..16w+15 are held by lanes 4w..4w+3)
         if ((lane >> 2) == gw) {
-          stg_v4(dst_sscale + c0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
-                                                 __float_as_uint(snew[2]), __float_as_uint(snew[3])));
+          stg_v4(dst_of(D_SSCALE) + c0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
+                                                       __float_as_uint(snew[2]), __float_as_uint(snew[3])));
           if (RSCALE == CARRY_SCALE_PER_V)
-            stg_v4(dst_rscale + c0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
+            stg_v4(dst_of(D_RSCALE) + c0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
                                                    __float_as_uint(esn[2]), __float_as_uint(esn[3])));
         }
-        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_rscale, __float_as_uint(esn[0]));
+        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_of(D_RSCALE), __float_as_uint(esn[0]));
       }
     }
     PROF_MARK(6)
