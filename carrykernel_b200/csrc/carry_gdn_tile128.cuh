@@ -189,6 +189,15 @@ __device__ __forceinline__ void s4x4_to_float(uint32_t w, float2& lo, float2& hi
   lo = add2(make_float2(__uint_as_float(a & 0xFFFFFF0Fu), __uint_as_float(b & 0xFFFFFF0Fu)), splat(-kMagicNib));
   hi16 = add2(make_float2(__uint_as_float(a & 0xFFFFFFF0u), __uint_as_float(b & 0xFFFFFFF0u)), splat(-kMagicByte));
 }
+// the same from a word whose low nibbles (wl = w & 0x0F0F0F0F) and high nibbles (wh = w & 0xF0F0F0F0)
+// were separated beforehand: two masks per word instead of four per byte pair
+template <int A, int B>
+__device__ __forceinline__ void s4x4_split_to_float(uint32_t wl, uint32_t wh, float2& lo, float2& hi16) {
+  lo = add2(make_float2(__uint_as_float(__byte_perm(wl, 0x4B000000u, 0x7440 | A)),
+                        __uint_as_float(__byte_perm(wl, 0x4B000000u, 0x7440 | B))), splat(-kMagicNib));
+  hi16 = add2(make_float2(__uint_as_float(__byte_perm(wh, 0x4B000000u, 0x7440 | A)),
+                          __uint_as_float(__byte_perm(wh, 0x4B000000u, 0x7440 | B))), splat(-kMagicByte));
+}
 // low bytes of four words -> one word (a | b<<8 | c<<16 | d<<24)
 __device__ __forceinline__ uint32_t pack4(uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   return __byte_perm(__byte_perm(a, b, 0x0040), __byte_perm(c, d, 0x0040), 0x5410);
@@ -803,12 +812,14 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             float am = 0.f;
             if constexpr (RES == CARRY_RES_INT4) {
               const uint2 rw = *reinterpret_cast<const uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2);
-              const uint32_t w[2] = {rw.x ^ 0x88888888u, rw.y ^ 0x88888888u};
+              const uint32_t wl[2] = {(rw.x ^ 0x88888888u) & 0x0F0F0F0Fu, (rw.y ^ 0x88888888u) & 0x0F0F0F0Fu};
+              const uint32_t wh[2] = {(rw.x ^ 0x88888888u) & 0xF0F0F0F0u, (rw.y ^ 0x88888888u) & 0xF0F0F0F0u};
               const float2 es2 = splat(es), es16 = splat(es * 0.0625f);
 #pragma unroll
               for (int m = 0; m < 4; ++m) {
                 float2 lo, hi;
-                if (m & 1) s4x4_to_float<2, 3>(w[m >> 1], lo, hi); else s4x4_to_float<0, 1>(w[m >> 1], lo, hi);
+                if (m & 1) s4x4_split_to_float<2, 3>(wl[m >> 1], wh[m >> 1], lo, hi);
+                else s4x4_split_to_float<0, 1>(wl[m >> 1], wh[m >> 1], lo, hi);
                 const float2 te = fma2(lo, es2, fma2(kE[m], dv2, hE[i][m]));
                 const float2 to = fma2(hi, es16, fma2(kO[m], dv2, hO[i][m]));
                 hE[i][m] = te; hO[i][m] = to;
