@@ -287,15 +287,16 @@ constexpr int kStaticKV = 24064;
 constexpr int kStaticOf(int layout) { return layout == 0 ? kStaticVK : kStaticKV; }
 constexpr int kSmemPerCta = 231424;     // one CTA per SM: 227 KB less 1 KB
 
-template <int RES, int LAYOUT, int QDT>
+template <int RES, int LAYOUT, int QDT, int RSCALE>
 struct StageLayout {
   static constexpr int kVecBytes = kT * (QDT == CARRY_F32 ? 4 : 2);
   static constexpr int kResidBytes = (RES == CARRY_RES_INT4) ? kT * kT / 2 : kT * kT;
   static constexpr int kCodes = 0;
   static constexpr int kResid = kT * kT;
   static constexpr int kSScale = kResid + kResidBytes;       // 128 floats
-  static constexpr int kRScale = kSScale + 512;              // 128 floats (per V) or a row of per-head scales
-  static constexpr int kQ = kRScale + 512;                   // raw q, k, v of this head
+  static constexpr int kRScale = kSScale + 512;              // 128 floats (per V), or the 16 bytes that hold
+  static constexpr int kRScaleBytes = (RSCALE == CARRY_SCALE_PER_V) ? 512 : 16;   // this head's scale (per head)
+  static constexpr int kQ = kRScale + ((RSCALE == CARRY_SCALE_PER_V) ? 512 : 128);   // raw q, k, v of this head
   static constexpr int kK = kQ + kVecBytes;
   static constexpr int kV = kK + kVecBytes;
   static constexpr int kBytes = kV + kVecBytes;
@@ -311,7 +312,10 @@ struct StageLayout {
   static constexpr int kStatic = kGroups * kStaticOf(LAYOUT);
   static constexpr int kBudget = kSmemPerCta - kStatic;
   static constexpr int kFit = kBudget / kBytes;
-  static constexpr int kStages = kFit > 5 * kGroups ? 5 * kGroups : kFit;
+  // a deeper ring does not help (a tile takes several times longer to compute than to load) and makes the
+  // burst of requests at the start of a launch larger: 6 stages measured best for two groups (5..8 tried)
+  static constexpr int kStageCap = (kGroups == 2) ? 6 : 5;
+  static constexpr int kStages = kFit > kStageCap ? kStageCap : kFit;
 };
 
 __device__ __forceinline__ int esize(int dtype) { return dtype == CARRY_F32 ? 4 : 2; }
@@ -427,7 +431,7 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
     a[D_SSCALE] = reinterpret_cast<unsigned long long>(p.sscale_out + slot * p.stride_sscale_slot + (long long)hv * kT);
     const float* rs = p.rscale_out + slot * p.stride_rscale_slot;
     a[D_RSCALE] = reinterpret_cast<unsigned long long>(rs + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : (long long)hv));
-    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(rs + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : 0));
+    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(rs + (RSCALE == CARRY_SCALE_PER_V ? (long long)hv * kT : (long long)(hv & ~3)));
     const uint8_t* row = reinterpret_cast<const uint8_t*>(p.q) + (long long)n * p.stride_mixed_tok * qes;
     a[D_Q] = reinterpret_cast<unsigned long long>(row + (long long)h * kT * qes);
     a[D_K] = reinterpret_cast<unsigned long long>(row + ((long long)p.H + h) * kT * qes);
@@ -437,7 +441,7 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
     a[D_RESID] = reinterpret_cast<unsigned long long>(reinterpret_cast<uint8_t*>(p.resid_out) + nh * RB);
     a[D_SSCALE] = reinterpret_cast<unsigned long long>(p.sscale_out + nh * kT);
     a[D_RSCALE] = reinterpret_cast<unsigned long long>(p.rscale_out + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : nh));
-    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(p.rscale_in + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : (long long)n * p.HV));
+    a[D_RSCALE_IN] = reinterpret_cast<unsigned long long>(p.rscale_in + (RSCALE == CARRY_SCALE_PER_V ? nh * kT : (nh & ~3LL)));
     a[D_Q] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.q) + nh * kT * qes);
     a[D_K] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.k) + nh * kT * qes);
     a[D_V] = reinterpret_cast<unsigned long long>(reinterpret_cast<const uint8_t*>(p.v) + nh * kT * qes);
@@ -524,8 +528,8 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
 // nothing is copied.
 template <int LAYOUT, int RES, int RSCALE, int QDT>
 __device__ __forceinline__ void issue_copies(const KParams& p, uint8_t* sb, uint64_t* bar, const unsigned long long (&a)[8]) {
-  using L = StageLayout<RES, LAYOUT, QDT>;
-  const uint32_t rscale_bytes = (RSCALE == CARRY_SCALE_PER_V) ? 512u : (uint32_t)p.HV * 4u;
+  using L = StageLayout<RES, LAYOUT, QDT, RSCALE>;
+  constexpr uint32_t rscale_bytes = L::kRScaleBytes;
   // launch-wide offsets from where results go to where the state is read (zero when in place)
   const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
   const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
@@ -563,9 +567,9 @@ __device__ __noinline__ void issue_cached(const KParams& p, uint8_t* sb, uint64_
 // the kernel
 // ---------------------------------------------------------------------------
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__global__ void __launch_bounds__(kThreads * StageLayout<RES, LAYOUT, QDT>::kGroups, 1)
+__global__ void __launch_bounds__(kThreads * StageLayout<RES, LAYOUT, QDT, RSCALE>::kGroups, 1)
 gdn_tile128_kernel(const __grid_constant__ KParams p) {
-  using L = StageLayout<RES, LAYOUT, QDT>;
+  using L = StageLayout<RES, LAYOUT, QDT, RSCALE>;
   constexpr int S = L::kStages;
   constexpr int G = L::kGroups;
   constexpr int kCache = kTileCache * G;
@@ -731,7 +735,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
                   q_mul = __uint_as_float(tm1.z), kq = __uint_as_float(tm1.w);
       const float* sscale = reinterpret_cast<const float*>(sb + L::kSScale);
       const float* rscale = reinterpret_cast<const float*>(sb + L::kRScale);
-      const float es_head = (RSCALE == CARRY_SCALE_PER_HEAD) ? rscale[hv] : 0.f;
+      const float es_head = (RSCALE == CARRY_SCALE_PER_HEAD) ? rscale[hv & 3] : 0.f;
       const float2 alpha2 = splat(alpha);
       const float2 magic2 = splat(kMagicRound), nmagic2 = splat(-kMagicRound);
 
@@ -1182,7 +1186,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 
 template <int LAYOUT, int RES, int RSCALE, int QDT>
 int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
-  using L = StageLayout<RES, LAYOUT, QDT>;
+  using L = StageLayout<RES, LAYOUT, QDT, RSCALE>;
   auto kern = gdn_tile128_kernel<LAYOUT, RES, RSCALE, QDT>;
   const size_t smem = (size_t)L::kBytes * L::kStages;
   static thread_local bool configured[64] = {false};
