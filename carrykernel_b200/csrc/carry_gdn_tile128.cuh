@@ -104,11 +104,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   if (!*poison) mbar_wait_slow(bar, parity, poison, status);
   return !*poison;
 }
-__device__ __forceinline__ int lds_i32(const void* p) {
-  int v;
-  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(smem_u32(p)) : "memory");
-  return v;
-}
 __device__ __forceinline__ uint4 lds_v4(const void* p) {
   uint4 v;
   asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
@@ -143,9 +138,6 @@ __device__ __forceinline__ uint32_t order_token() {
   uint32_t t;
   asm volatile("mov.u32 %0, 0;" : "=r"(t) : : "memory");
   return t;
-}
-__device__ __forceinline__ void stg_v2(unsigned long long addr, uint2 v) {
-  asm volatile("st.global.v2.b32 [%0], {%1, %2};" ::"l"(addr), "r"(v.x), "r"(v.y) : "memory");
 }
 __device__ __forceinline__ void stg_b32(unsigned long long addr, uint32_t v) {
   asm volatile("st.global.b32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
@@ -270,11 +262,6 @@ __device__ __forceinline__ float scale_fast(float amax, float qmax, float rq, in
   return fmaxf(div_qmax(amax, qmax, rq), kEps);
 }
 
-__device__ __forceinline__ float warp_sum32(float x) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
-  return x;
-}
 
 // ---------------------------------------------------------------------------
 // shared-memory stage layout (bytes)
@@ -318,13 +305,7 @@ struct StageLayout {
   static constexpr int kStages = kFit > kStageCap ? kStageCap : kFit;
 };
 
-__device__ __forceinline__ int esize(int dtype) { return dtype == CARRY_F32 ? 4 : 2; }
 
-__device__ __forceinline__ float raw_to_float(const uint8_t* base, int i, int dtype) {
-  if (dtype == CARRY_F32) return reinterpret_cast<const float*>(base)[i];
-  if (dtype == CARRY_BF16) return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(base)[i]);
-  return __half2float(reinterpret_cast<const __half*>(base)[i]);
-}
 
 
 // activations of one head as they sit in the stage (element type QDT) -> fp32
