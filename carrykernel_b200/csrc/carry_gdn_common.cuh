@@ -21,6 +21,9 @@ constexpr float kSoftplusThreshold = 20.0f;
 struct KParams {
   int packed;
   int B, H, HV, K, V;
+  int hv_shift;      // log2(HV) when HV is a power of two, else -1       (filled by tile128's launcher;
+  int group;         // value heads per key head, HV / H                    the streaming kernel splits tile
+  int group_shift;   // log2(group) when that is a power of two, else -1    indices without dividing)
   float qmax;
   int res_fmt, rscale_mode, sscale_mode, eps_mode;
   int qkv_dtype, o_dtype;

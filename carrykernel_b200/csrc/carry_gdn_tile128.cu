@@ -50,7 +50,12 @@ int launch_tile128(const KParams& p, cudaStream_t stream) {
       return CARRY_GDN_ERR_NO_DEVICE;
     }
   }
-  return p.packed ? launch_tile128_vk(p, stream, sms[dev]) : launch_tile128_kv(p, stream, sms[dev]);
+  KParams q = p;
+  auto log2_or_minus1 = [](int x) { int s = 0; while ((1 << s) < x) ++s; return (1 << s) == x ? s : -1; };
+  q.hv_shift = log2_or_minus1(p.HV);
+  q.group = p.HV / p.H;
+  q.group_shift = log2_or_minus1(q.group);
+  return q.packed ? launch_tile128_vk(q, stream, sms[dev]) : launch_tile128_kv(q, stream, sms[dev]);
 }
 
 }  // namespace carry

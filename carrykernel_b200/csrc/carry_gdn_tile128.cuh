@@ -300,7 +300,7 @@ struct StageLayout {
   static constexpr int kBudget = kSmemPerCta - kStatic;
   static constexpr int kFit = kBudget / kBytes;
   // a deeper ring does not help (a tile takes several times longer to compute than to load) and makes the
-  // burst of requests at the start of a launch larger: 6 stages measured best for two groups (5..8 tried)
+  // burst of requests at the start of a launch larger: 6 stages measured best for two groups (4..8 tried)
   static constexpr int kStageCap = (kGroups == 2) ? 6 : 5;
   static constexpr int kStages = kFit > kStageCap ? kStageCap : kFit;
 };
@@ -381,6 +381,13 @@ __device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float&
   }
 }
 
+// tile index -> request row, value head, key head; shifts when the head counts are powers of two
+__device__ __forceinline__ void split_tile(const KParams& p, int tile, int& n, int& hv, int& h) {
+  if (p.hv_shift >= 0) { n = tile >> p.hv_shift; hv = tile & (p.HV - 1); }
+  else { n = tile / p.HV; hv = tile - n * p.HV; }
+  h = !p.packed ? hv : (p.group_shift >= 0 ? (hv >> p.group_shift) : hv / p.group);
+}
+
 // What a CTA needs to know about one of its tiles before the data arrives.
 struct __align__(16) TileMeta {
   int n, hv_h, slot;    // hv_h: value head in the low 16 bits, its key head above them
@@ -440,9 +447,8 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
   TileMeta m;
-  m.n = tile / p.HV;
-  const int hv = tile - m.n * p.HV;
-  const int h = p.packed ? hv / (p.HV / p.H) : hv;
+  int hv, h;
+  split_tile(p, tile, m.n, hv, h);
   m.hv_h = hv | (h << 16);
   long long q_off, k_off;
   if (p.packed) {
@@ -604,12 +610,15 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #ifdef CARRY_PROFILE
   const long long prof_p1 = clock64();
 #endif
-  if (lane == 0 && warp < G && warp < my_tiles) {
-    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
-    const int tn = tile / p.HV, thv = tile - tn * p.HV;
-    const int th = p.packed ? thv / (p.HV / p.H) : thv;
+  // (the last warps make these requests: the first warps are the ones with tiles to prepare when a CTA
+  // has few, and a request worked out from scratch is a long chain of one thread's instructions)
+  if (lane == 0 && warp >= G * kWarps - G && (G * kWarps - 1 - warp) < my_tiles) {
+    const int num = G * kWarps - 1 - warp;
+    const int tile = (int)blockIdx.x + num * (int)gridDim.x;
+    int tn, thv, th;
+    split_tile(p, tile, tn, thv, th);
     const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)warp * L::kBytes, &full_bar[warp], tn, thv, th, tslot);
+    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], tn, thv, th, tslot);
   }
   __syncwarp();
 #ifdef CARRY_PROFILE
@@ -619,8 +628,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
     const int i = tid >> 2;
     const bool valid = i < my_tiles;
-    tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
-                                 &meta_cache[i], &desc_cache[i]);
+    if (warp * 8 < my_tiles)                         // warps without a tile to prepare stay out of the way
+      tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
+                                   &meta_cache[i], &desc_cache[i]);
   }
 #ifdef CARRY_PROFILE
   const long long prof_p3 = clock64();
@@ -639,8 +649,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       issue_cached<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], &desc_cache[num], meta_cache[num].slot);
     } else {
       const int tile = (int)blockIdx.x + num * (int)gridDim.x;
-      const int tn = tile / p.HV, thv = tile - tn * p.HV;
-      const int th = p.packed ? thv / (p.HV / p.H) : thv;
+      int tn, thv, th;
+      split_tile(p, tile, tn, thv, th);
       const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
       issue_tile<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], tn, thv, th, tslot);
     }
