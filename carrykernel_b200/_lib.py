@@ -14,7 +14,7 @@ import torch
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libcarry_gdn.so")
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 F32, BF16, F16 = 0, 1, 2
 RES_FP32, RES_FP16, RES_FP8, RES_INT8, RES_INT4, RES_NONE = 0, 1, 2, 3, 4, 5
@@ -72,8 +72,18 @@ class PackedArgs(C.Structure):
     ]
 
 
+class PackedMultiArgs(C.Structure):
+    _fields_ = [
+        ("step", PackedArgs), ("T", C.c_int32),
+        ("stride_mixed_t", C.c_int64), ("stride_a_t", C.c_int64), ("stride_b_t", C.c_int64),
+    ]
+
+
+ERR_UNSUPPORTED = -5
+
 EXPORTS = ("carry_gdn_quant_step", "carry_gdn_fp32_step", "carry_gdn_packed_decode",
-           "carry_gdn_strerror", "carry_gdn_abi_version", "carry_gdn_last_kernel")
+           "carry_gdn_packed_decode_multi", "carry_gdn_strerror", "carry_gdn_abi_version",
+           "carry_gdn_last_kernel")
 
 _lib = None
 _lock = threading.Lock()
@@ -105,7 +115,9 @@ def load_library(path: str | None = None):
         lib.carry_gdn_quant_step.argtypes = [C.POINTER(StepArgs), C.c_void_p]
         lib.carry_gdn_fp32_step.argtypes = [C.POINTER(Fp32Args), C.c_void_p]
         lib.carry_gdn_packed_decode.argtypes = [C.POINTER(PackedArgs), C.c_void_p]
-        for fn in (lib.carry_gdn_quant_step, lib.carry_gdn_fp32_step, lib.carry_gdn_packed_decode):
+        lib.carry_gdn_packed_decode_multi.argtypes = [C.POINTER(PackedMultiArgs), C.c_void_p]
+        for fn in (lib.carry_gdn_quant_step, lib.carry_gdn_fp32_step, lib.carry_gdn_packed_decode,
+                   lib.carry_gdn_packed_decode_multi):
             fn.restype = C.c_int
         if lib.carry_gdn_abi_version() != ABI_VERSION:
             raise CudaUnavailable(

@@ -24,6 +24,58 @@ int dispatch(const carry::KParams& p, cudaStream_t stream) {
 
 }  // namespace
 
+namespace carry {
+// Checks the arguments of the slot-indexed call and turns them into kernel parameters.
+int packed_params(const CarryGdnPackedArgs* a, KParams& p) {
+  if (!a) return CARRY_GDN_ERR_NULL;
+  if (a->B < 0 || a->H <= 0 || a->HV <= 0 || a->K <= 0 || a->V <= 0 || a->num_slots < 0)
+    return CARRY_GDN_ERR_SHAPE;
+  if (a->HV % a->H != 0) return CARRY_GDN_ERR_SHAPE;
+  if (!(a->qmax >= 1.0f && a->qmax <= 127.0f)) return CARRY_GDN_ERR_SHAPE;
+  if (!dtype_ok(a->qkv_dtype) || !dtype_ok(a->out_dtype) || !dtype_ok(a->ab_dtype) ||
+      !dtype_ok(a->A_log_dtype) || !dtype_ok(a->dt_bias_dtype))
+    return CARRY_GDN_ERR_DTYPE;
+  if (a->res_fmt != CARRY_RES_INT8 && a->res_fmt != CARRY_RES_INT4) return CARRY_GDN_ERR_FORMAT;
+  if (!scale_mode_ok(a->resid_scale_mode) || !eps_ok(a->eps_mode)) return CARRY_GDN_ERR_FORMAT;
+  if (a->res_fmt == CARRY_RES_INT4 && (a->K & 1)) return CARRY_GDN_ERR_FORMAT;
+  if (a->B == 0) return CARRY_GDN_OK;   // nothing to do; p is not filled
+  if (!a->mixed_qkv || !a->a || !a->b || !a->A_log || !a->dt_bias || !a->state_codes ||
+      !a->state_scale || !a->resid_codes || !a->resid_scale || !a->out || !a->ssm_state_indices)
+    return CARRY_GDN_ERR_NULL;
+
+  p = carry::KParams{};
+  p.packed = 1;
+  p.B = a->B; p.H = a->H; p.HV = a->HV; p.K = a->K; p.V = a->V;
+  p.qmax = a->qmax;
+  p.res_fmt = a->res_fmt; p.rscale_mode = a->resid_scale_mode; p.sscale_mode = CARRY_SCALE_PER_V;
+  p.eps_mode = a->eps_mode;
+  p.qkv_dtype = a->qkv_dtype; p.o_dtype = a->out_dtype;
+  p.status = a->status;
+  p.codes_in = a->state_codes; p.codes_out = a->state_codes;
+  p.sscale_in = a->state_scale; p.sscale_out = a->state_scale;
+  p.resid_in = a->resid_codes; p.resid_out = a->resid_codes;
+  p.rscale_in = a->resid_scale; p.rscale_out = a->resid_scale;
+  p.stride_state_slot = a->stride_state_slot; p.stride_resid_slot = a->stride_resid_slot;
+  p.stride_sscale_slot = a->stride_sscale_slot; p.stride_rscale_slot = a->stride_rscale_slot;
+  p.q = a->mixed_qkv; p.k = a->mixed_qkv; p.v = a->mixed_qkv;
+  p.stride_mixed_tok = a->stride_mixed_tok;
+  p.a = a->a; p.b = a->b; p.stride_a_tok = a->stride_a_tok; p.stride_b_tok = a->stride_b_tok;
+  p.ab_dtype = a->ab_dtype;
+  p.A_log = a->A_log; p.dt_bias = a->dt_bias;
+  p.A_log_dtype = a->A_log_dtype; p.dt_bias_dtype = a->dt_bias_dtype;
+  p.qscale = a->scale;
+  p.l2norm = a->use_qk_l2norm;
+  p.slot_idx = a->ssm_state_indices; p.stride_idx = a->stride_indices;
+  p.num_slots = a->num_slots;
+  p.out = a->out;
+#ifdef CARRY_PROFILE
+  p.prof = reinterpret_cast<long long*>(a->status);   // debug builds reuse the status pointer (8 x int64)
+  p.status = nullptr;
+#endif
+  return CARRY_GDN_OK;
+}
+}  // namespace carry
+
 extern "C" {
 
 int carry_gdn_abi_version(void) { return CARRY_GDN_ABI_VERSION; }
@@ -94,52 +146,24 @@ int carry_gdn_fp32_step(const CarryGdnFp32Args* a, void* stream) {
 }
 
 int carry_gdn_packed_decode(const CarryGdnPackedArgs* a, void* stream) {
-  if (!a) return CARRY_GDN_ERR_NULL;
-  if (a->B < 0 || a->H <= 0 || a->HV <= 0 || a->K <= 0 || a->V <= 0 || a->num_slots < 0)
-    return CARRY_GDN_ERR_SHAPE;
-  if (a->HV % a->H != 0) return CARRY_GDN_ERR_SHAPE;
-  if (!(a->qmax >= 1.0f && a->qmax <= 127.0f)) return CARRY_GDN_ERR_SHAPE;
-  if (!dtype_ok(a->qkv_dtype) || !dtype_ok(a->out_dtype) || !dtype_ok(a->ab_dtype) ||
-      !dtype_ok(a->A_log_dtype) || !dtype_ok(a->dt_bias_dtype))
-    return CARRY_GDN_ERR_DTYPE;
-  if (a->res_fmt != CARRY_RES_INT8 && a->res_fmt != CARRY_RES_INT4) return CARRY_GDN_ERR_FORMAT;
-  if (!scale_mode_ok(a->resid_scale_mode) || !eps_ok(a->eps_mode)) return CARRY_GDN_ERR_FORMAT;
-  if (a->res_fmt == CARRY_RES_INT4 && (a->K & 1)) return CARRY_GDN_ERR_FORMAT;
-  if (a->B == 0) return CARRY_GDN_OK;
-  if (!a->mixed_qkv || !a->a || !a->b || !a->A_log || !a->dt_bias || !a->state_codes ||
-      !a->state_scale || !a->resid_codes || !a->resid_scale || !a->out || !a->ssm_state_indices)
-    return CARRY_GDN_ERR_NULL;
-
-  carry::KParams p = {};
-  p.packed = 1;
-  p.B = a->B; p.H = a->H; p.HV = a->HV; p.K = a->K; p.V = a->V;
-  p.qmax = a->qmax;
-  p.res_fmt = a->res_fmt; p.rscale_mode = a->resid_scale_mode; p.sscale_mode = CARRY_SCALE_PER_V;
-  p.eps_mode = a->eps_mode;
-  p.qkv_dtype = a->qkv_dtype; p.o_dtype = a->out_dtype;
-  p.status = a->status;
-  p.codes_in = a->state_codes; p.codes_out = a->state_codes;
-  p.sscale_in = a->state_scale; p.sscale_out = a->state_scale;
-  p.resid_in = a->resid_codes; p.resid_out = a->resid_codes;
-  p.rscale_in = a->resid_scale; p.rscale_out = a->resid_scale;
-  p.stride_state_slot = a->stride_state_slot; p.stride_resid_slot = a->stride_resid_slot;
-  p.stride_sscale_slot = a->stride_sscale_slot; p.stride_rscale_slot = a->stride_rscale_slot;
-  p.q = a->mixed_qkv; p.k = a->mixed_qkv; p.v = a->mixed_qkv;
-  p.stride_mixed_tok = a->stride_mixed_tok;
-  p.a = a->a; p.b = a->b; p.stride_a_tok = a->stride_a_tok; p.stride_b_tok = a->stride_b_tok;
-  p.ab_dtype = a->ab_dtype;
-  p.A_log = a->A_log; p.dt_bias = a->dt_bias;
-  p.A_log_dtype = a->A_log_dtype; p.dt_bias_dtype = a->dt_bias_dtype;
-  p.qscale = a->scale;
-  p.l2norm = a->use_qk_l2norm;
-  p.slot_idx = a->ssm_state_indices; p.stride_idx = a->stride_indices;
-  p.num_slots = a->num_slots;
-  p.out = a->out;
-#ifdef CARRY_PROFILE
-  p.prof = reinterpret_cast<long long*>(a->status);   // debug builds reuse the status pointer (8 x int64)
-  p.status = nullptr;
-#endif
+  carry::KParams p;
+  const int rc = carry::packed_params(a, p);
+  if (rc != CARRY_GDN_OK || a->B == 0) return rc;
   return dispatch(p, static_cast<cudaStream_t>(stream));
+}
+
+int carry_gdn_packed_decode_multi(const CarryGdnPackedMultiArgs* m, void* stream) {
+  if (!m) return CARRY_GDN_ERR_NULL;
+  if (m->T < 1) return CARRY_GDN_ERR_SHAPE;
+  carry::KParams p;
+  const int rc = carry::packed_params(&m->step, p);
+  if (rc != CARRY_GDN_OK || m->step.B == 0) return rc;
+  const int qes = p.qkv_dtype == CARRY_F32 ? 4 : 2;
+  if (!carry::tile128_eligible(p) || (m->stride_mixed_t * qes) % 16) return CARRY_GDN_ERR_UNSUPPORTED;
+  const int rc2 = carry::launch_multi(p, m->T, m->stride_mixed_t, m->stride_a_t, m->stride_b_t,
+                                      static_cast<cudaStream_t>(stream));
+  if (rc2 == CARRY_GDN_OK) g_last_kernel = 3;
+  return rc2;
 }
 
 }  // extern "C"

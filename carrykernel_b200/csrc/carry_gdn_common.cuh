@@ -188,5 +188,7 @@ int launch_generic(const KParams& p, cudaStream_t stream);
 int launch_fp32(const CarryGdnFp32Args& a, cudaStream_t stream);
 bool tile128_eligible(const KParams& p);
 int launch_tile128(const KParams& p, cudaStream_t stream);
+int launch_multi(const KParams& p, int T, long long stride_mixed_t, long long stride_a_t, long long stride_b_t,
+                 cudaStream_t stream);
 
 }  // namespace carry

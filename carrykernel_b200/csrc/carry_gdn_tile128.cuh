@@ -369,10 +369,11 @@ __device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float 
 }
 
 // gates of one (request, head): derived in the kernel on the slot path, given on the other
-__device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta) {
+__device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta,
+                                         long long tok_a = 0, long long tok_b = 0) {
   if (p.packed) {
-    slot_gates(load_as_float(p.a, (long long)n * p.stride_a_tok + hv, p.ab_dtype),
-               load_as_float(p.b, (long long)n * p.stride_b_tok + hv, p.ab_dtype),
+    slot_gates(load_as_float(p.a, (long long)n * p.stride_a_tok + hv + tok_a, p.ab_dtype),
+               load_as_float(p.b, (long long)n * p.stride_b_tok + hv + tok_b, p.ab_dtype),
                load_as_float(p.A_log, hv, p.A_log_dtype), load_as_float(p.dt_bias, hv, p.dt_bias_dtype),
                alpha, beta);
   } else {
@@ -442,8 +443,11 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
 // lanes of a warp must call this together; when `store` is set the first lane of a group writes `dst`
 // and each of the four lanes a quarter of the tile's addresses to `ddst`.  A slot id beyond the pool is
 // reported in the status word and treated as padding.
+// (tok_*: element offsets of the token within its request, for callers that take several tokens per
+// request; `ddst` may be null.)
 template <int RES, int RSCALE, int QDT>
-__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst) {
+__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst,
+                                        long long tok_qkv = 0, long long tok_a = 0, long long tok_b = 0) {
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
   TileMeta m;
@@ -452,7 +456,7 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
   m.hv_h = hv | (h << 16);
   long long q_off, k_off;
   if (p.packed) {
-    q_off = (long long)m.n * p.stride_mixed_tok + (long long)h * kT;
+    q_off = (long long)m.n * p.stride_mixed_tok + (long long)h * kT + tok_qkv;
     k_off = q_off + (long long)p.H * kT;
   } else {
     q_off = k_off = ((long long)m.n * p.HV + hv) * kT;
@@ -463,7 +467,7 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) { qv[j] = __ldg(qp + j); kv[j] = __ldg(kp + j); }
   m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
-  gates_of(p, m.n, hv, m.alpha, m.beta);
+  gates_of(p, m.n, hv, m.alpha, m.beta, tok_a, tok_b);
   float ks = 0.f, qs = 0.f, kq = 0.f;
 #pragma unroll
   for (int j = 0; j < kVecs; ++j) {
@@ -499,8 +503,8 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
     if (store && sub == 0 && p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
     m.slot = 0;
   }
-  if (store) {
-    if (sub == 0) *dst = m;
+  if (store && sub == 0) *dst = m;
+  if (store && ddst) {
     unsigned long long a[8];
     tile_addresses<RES, RSCALE, QDT>(p, m.n, hv, h, m.slot > 0 ? m.slot : 0, a);
     const unsigned long long lo = (sub == 0) ? a[0] : (sub == 1) ? a[2] : (sub == 2) ? a[4] : a[6];
@@ -731,250 +735,59 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       const float2 magic2 = splat(kMagicRound), nmagic2 = splat(-kMagicRound);
 
       if constexpr (LAYOUT == LAYOUT_VK) {
-        // lane: rows r0..r0+3, columns c0..c0+15.  A quad of columns (one 32-bit
-        // word of codes) is held as two pairs: E = {col 0, col 2}, O = {col 1, col 3}.
-        const int cg = lane & 7, rg = lane >> 3;
-        const int r0 = 16 * gw + 4 * rg, c0 = 16 * cg;
-        float* qw = q_warp + warp * kT;
-        {   // this warp's copy of q: fp32, scaled, each quad stored as {q0, q2, q1, q3}.  Quad j = 4 cg + m
-            // sits at position 8 m + cg, so that the 8 lanes of a row group read 128 contiguous bytes.
-          const float4 q4 = act4<QDT>(sb + L::kQ, 4 * lane);
-          *reinterpret_cast<float4*>(qw + 4 * (8 * (lane & 3) + (lane >> 2))) =
-              make_float4(q4.x * q_mul, q4.z * q_mul, q4.y * q_mul, q4.w * q_mul);
-        }
-        float2 kE[4], kO[4];
-        act16_pairs<QDT>(sb + L::kK, c0, k_mul, kE, kO);
-        __syncwarp();
-        const uint32_t q_token = order_token();
-
-        float2 hE[4][4], hO[4][4];       // [row][quad]
-        float dk[4], dq[4];
-        // phase 1: dequantise, decay, partial dot products along the row
-        {
-          const float4 s4 = *reinterpret_cast<const float4*>(sscale + r0);
-          const float srow[4] = {s4.x, s4.y, s4.z, s4.w};
-          const uint32_t q_addr = smem_u32(qw + 4 * cg) + q_token;
-          auto q_quad = [&](int row, int m) -> float4 {
-#define CARRY_Q_ROW(R)                                                                                    \
-  ((m == 0) ? lds_f4_at<0, R>(q_addr) : (m == 1) ? lds_f4_at<128, R>(q_addr)                              \
-                                      : (m == 2) ? lds_f4_at<256, R>(q_addr) : lds_f4_at<384, R>(q_addr))
-            return (row == 0) ? CARRY_Q_ROW(0) : (row == 1) ? CARRY_Q_ROW(1) : (row == 2) ? CARRY_Q_ROW(2) : CARRY_Q_ROW(3);
-#undef CARRY_Q_ROW
-          };
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const uint4 cw = *reinterpret_cast<const uint4*>(sb + L::kCodes + (r0 + i) * kT + c0);
-            const uint32_t w[4] = {cw.x ^ 0x80808080u, cw.y ^ 0x80808080u, cw.z ^ 0x80808080u, cw.w ^ 0x80808080u};
-            const float2 s2 = splat(srow[i]);
-            float2 ak = make_float2(0.f, 0.f), aq = make_float2(0.f, 0.f);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const float2 e = mul2(mul2(s8x2_to_float<0, 2>(w[m]), s2), alpha2);
-              const float2 o = mul2(mul2(s8x2_to_float<1, 3>(w[m]), s2), alpha2);
-              hE[i][m] = e; hO[i][m] = o;
-              // re-read per row on purpose: q must not stay in registers
-              const float4 qq = q_quad(i, m);
-              const float2 qe = make_float2(qq.x, qq.y), qo = make_float2(qq.z, qq.w);
-              ak = fma2(e, kE[m], ak); ak = fma2(o, kO[m], ak);
-              aq = fma2(e, qe, aq); aq = fma2(o, qo, aq);
-            }
-            dk[i] = ak.x + ak.y; dq[i] = aq.x + aq.y;
-          }
-        }
-        PROF_MARK(1)
-        // lane cg of a row group ends up with one total: <h row, k> of row cg (cg < 4) or <h row, q> of
-        // row cg - 4; the four k totals are then handed to every lane of the group
-        const float dot_mine = group_sum8_transposed(dk, dq, cg);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) dk[i] = __shfl_sync(0xffffffffu, dot_mine, (lane & 24) + i);
-        PROF_MARK(2)
-
-        // phase 2: rank-1 write and residual, each one fused multiply-add; row maxima
-        float amax[4], dvr[4];
-        {
-          const float4 v4 = act4<QDT>(sb + L::kV, r0);
-          dvr[0] = __fmul_rn(beta, __fadd_rn(v4.x, -dk[0])); dvr[1] = __fmul_rn(beta, __fadd_rn(v4.y, -dk[1]));
-          dvr[2] = __fmul_rn(beta, __fadd_rn(v4.z, -dk[2])); dvr[3] = __fmul_rn(beta, __fadd_rn(v4.w, -dk[3]));
-          if (cg >= 4) {                      // the lanes that hold a q total finish that row's output
-            const int i = cg & 3;
-            const float dv_i = (i == 0) ? dvr[0] : (i == 1) ? dvr[1] : (i == 2) ? dvr[2] : dvr[3];
-            store_from_float(p.out, (long long)out_row * kT + r0 + i, p.o_dtype, fmaf(dv_i, kq, dot_mine));
-          }
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 dv2 = splat(dvr[i]);
-            const float es = (RSCALE == CARRY_SCALE_PER_V) ? rscale[r0 + i] : es_head;
-            float am = 0.f;
-            if constexpr (RES == CARRY_RES_INT4) {
-              const uint2 rw = *reinterpret_cast<const uint2*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2);
-              const uint32_t wl[2] = {(rw.x ^ 0x88888888u) & 0x0F0F0F0Fu, (rw.y ^ 0x88888888u) & 0x0F0F0F0Fu};
-              const uint32_t wh[2] = {(rw.x ^ 0x88888888u) & 0xF0F0F0F0u, (rw.y ^ 0x88888888u) & 0xF0F0F0F0u};
-              const float2 es2 = splat(es), es16 = splat(es * 0.0625f);
-#pragma unroll
-              for (int m = 0; m < 4; ++m) {
-                float2 lo, hi;
-                if (m & 1) s4x4_split_to_float<2, 3>(wl[m >> 1], wh[m >> 1], lo, hi);
-                else s4x4_split_to_float<0, 1>(wl[m >> 1], wh[m >> 1], lo, hi);
-                const float2 te = fma2(lo, es2, fma2(kE[m], dv2, hE[i][m]));
-                const float2 to = fma2(hi, es16, fma2(kO[m], dv2, hO[i][m]));
-                hE[i][m] = te; hO[i][m] = to;
-                am = max3abs(max3abs(am, te), to);
-              }
-            } else {
-              const uint4 rw = *reinterpret_cast<const uint4*>(sb + L::kResid + (r0 + i) * kT + c0);
-              const uint32_t w[4] = {rw.x ^ 0x80808080u, rw.y ^ 0x80808080u, rw.z ^ 0x80808080u, rw.w ^ 0x80808080u};
-              const float2 es2 = splat(es);
-#pragma unroll
-              for (int m = 0; m < 4; ++m) {
-                const float2 te = fma2(s8x2_to_float<0, 2>(w[m]), es2, fma2(kE[m], dv2, hE[i][m]));
-                const float2 to = fma2(s8x2_to_float<1, 3>(w[m]), es2, fma2(kO[m], dv2, hO[i][m]));
-                hE[i][m] = te; hO[i][m] = to;
-                am = max3abs(max3abs(am, te), to);
-              }
-            }
-            amax[i] = am;
-          }
-        }
-        // new state scales: lanes 2i, 2i+1 of a row group end up with row i's maximum and derive its
-        // scale and reciprocal, which are then handed to the whole group
-        float snew[4], sinv[4];
-        {
-          const float s_mine = scale_fast(group_max4_transposed(amax, cg), p.qmax, rqmax_state, p.eps_mode);
-          const float i_mine = rcp_refined(s_mine);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            snew[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + 2 * i);
-            sinv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + 2 * i);
-          }
-        }
-        PROF_MARK(3)
-        if (cg == 0) stg_v4(dst_of(D_SSCALE) + r0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
-                                                            __float_as_uint(snew[2]), __float_as_uint(snew[3])));
-        // phase 3: state codes, new residual.  target - code * scale is one fused multiply-add, which is
-        // exact here (the difference of two nearly equal numbers), so the target can be rebuilt from the
-        // remainder when a row has to be re-decided.  No branch until all four rows are done.
-        float eamax[4];
-        uint32_t cw[4][4];
-        float worst = -1.0f;                 // max over rows of (largest remainder - tie guard)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 inv2 = splat(sinv[i]), ns2 = splat(-snew[i]);
-          float emA = 0.f, emB = 0.f;
-#pragma unroll
-          for (int m = 0; m < 4; ++m) {
-            const float2 yE = fma2(hE[i][m], inv2, magic2);
-            const float2 yO = fma2(hO[i][m], inv2, magic2);
-            hE[i][m] = fma2(add2(yE, nmagic2), ns2, hE[i][m]);
-            hO[i][m] = fma2(add2(yO, nmagic2), ns2, hO[i][m]);
-            emA = max3abs(emA, hE[i][m]);
-            emB = max3abs(emB, hO[i][m]);
-            cw[i][m] = pack4(__float_as_uint(yE.x), __float_as_uint(yO.x), __float_as_uint(yE.y), __float_as_uint(yO.y));
-          }
-          eamax[i] = fmaxf(emA, emB);
-          worst = fmaxf(worst, fmaf(-snew[i], kTieGuard, eamax[i]));
-        }
-        if (worst > 0.f) {                   // rare: some quotient within the tie guard
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float thr = snew[i] * kTieGuard;
-            if (eamax[i] > thr) {
-              float em = 0.f;
-#pragma unroll
-              for (int m = 0; m < 4; ++m) {
-                float2 yE = add2(s8x2_to_float<0, 2>(cw[i][m] ^ 0x80808080u), magic2);
-                float2 yO = add2(s8x2_to_float<1, 3>(cw[i][m] ^ 0x80808080u), magic2);
-                redecide_rec(hE[i][m].x, yE.x, snew[i], thr); redecide_rec(hE[i][m].y, yE.y, snew[i], thr);
-                redecide_rec(hO[i][m].x, yO.x, snew[i], thr); redecide_rec(hO[i][m].y, yO.y, snew[i], thr);
-                em = max3abs(max3abs(em, hE[i][m]), hO[i][m]);
-                cw[i][m] = pack4(__float_as_uint(yE.x), __float_as_uint(yO.x), __float_as_uint(yE.y), __float_as_uint(yO.y));
-              }
-              eamax[i] = em;
-            }
-          }
-        }
-        {
-          const unsigned long long base = dst_of(D_CODES) + r0 * kT + c0;
-          stg_v4_at<0 * kT>(base, make_uint4(cw[0][0], cw[0][1], cw[0][2], cw[0][3]));
-          stg_v4_at<1 * kT>(base, make_uint4(cw[1][0], cw[1][1], cw[1][2], cw[1][3]));
-          stg_v4_at<2 * kT>(base, make_uint4(cw[2][0], cw[2][1], cw[2][2], cw[2][3]));
-          stg_v4_at<3 * kT>(base, make_uint4(cw[3][0], cw[3][1], cw[3][2], cw[3][3]));
-        }
-        PROF_MARK(4)
-
-        // phase 4: residual scale and codes
-        float esn[4], einv[4];
-        if constexpr (RSCALE == CARRY_SCALE_PER_V) {
-          if (lane == 0) claim_next(cnt);      // no data crosses warps here: the meeting only hands on the stage
-          warps_meet(bar0 + 3);
-          refill_stage(cnt, it);
-          PROF_MARK(5)
-          const float s_mine = scale_fast(group_max4_transposed(eamax, cg), rqmax, rrqmax, p.eps_mode);
-          const float i_mine = rcp_refined(s_mine);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            esn[i] = __shfl_sync(0xffffffffu, s_mine, (lane & 24) + 2 * i);
-            einv[i] = __shfl_sync(0xffffffffu, i_mine, (lane & 24) + 2 * i);
-          }
-        } else {
-          const float m4 = warp_max_nonneg(fmaxf(fmaxf(eamax[0], eamax[1]), fmaxf(eamax[2], eamax[3])));
-          if (lane == 0) { head_red[grp][cnt & 1][gw] = m4; claim_next(cnt); }
-          warps_meet(bar0 + 3);
-          refill_stage(cnt, it);
-          PROF_MARK(5)
-          float m = head_red[grp][cnt & 1][0];
-#pragma unroll
-          for (int w = 1; w < kWarps; ++w) m = fmaxf(m, head_red[grp][cnt & 1][w]);
-          const float e1 = scale_fast(m, rqmax, rrqmax, p.eps_mode);
-          const float i1 = rcp_refined(e1);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) { esn[i] = e1; einv[i] = i1; }
-        }
-        const unsigned long long dst_resid = dst_of(D_RESID);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 invE = splat(einv[i]);
-          if constexpr (RES == CARRY_RES_INT4) {
-            // even columns: rint(e/es) + 8 + 128 lands in the low mantissa bits; 16 * rint(e/es) of the odd
-            // column is added on top, so the low byte of the sum is (odd + 8) << 4 | (even + 8); the final
-            // XOR removes the bias of both nibbles.
-            const float2 mE = splat(kMagicRound + 136.0f), sixteen = splat(16.0f);
-            uint32_t by[8];
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const float2 ye = fma2(hE[i][m], invE, mE);
-              const float2 co = add2(fma2(hO[i][m], invE, magic2), nmagic2);
-              const float2 pk = fma2(co, sixteen, ye);
-              by[2 * m] = __float_as_uint(pk.x);
-              by[2 * m + 1] = __float_as_uint(pk.y);
-            }
-            const uint32_t w0 = pack4(by[0], by[1], by[2], by[3]) ^ 0x88888888u;
-            const uint32_t w1 = pack4(by[4], by[5], by[6], by[7]) ^ 0x88888888u;
-            const unsigned long long base = dst_resid + r0 * (kT / 2) + c0 / 2;
-            if (i == 0) stg_v2_at<0 * (kT / 2)>(base, make_uint2(w0, w1));
-            if (i == 1) stg_v2_at<1 * (kT / 2)>(base, make_uint2(w0, w1));
-            if (i == 2) stg_v2_at<2 * (kT / 2)>(base, make_uint2(w0, w1));
-            if (i == 3) stg_v2_at<3 * (kT / 2)>(base, make_uint2(w0, w1));
-          } else {
-            uint32_t packed[4];
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-              const float2 ye = fma2(hE[i][m], invE, magic2);
-              const float2 yo = fma2(hO[i][m], invE, magic2);
-              packed[m] = pack4(__float_as_uint(ye.x), __float_as_uint(yo.x), __float_as_uint(ye.y),
-                                __float_as_uint(yo.y));
-            }
-            const unsigned long long base = dst_resid + r0 * kT + c0;
-            const uint4 pw = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            if (i == 0) stg_v4_at<0 * kT>(base, pw);
-            if (i == 1) stg_v4_at<1 * kT>(base, pw);
-            if (i == 2) stg_v4_at<2 * kT>(base, pw);
-            if (i == 3) stg_v4_at<3 * kT>(base, pw);
-          }
-        }
-        if (RSCALE == CARRY_SCALE_PER_V && cg == 0)
-          stg_v4(dst_of(D_RSCALE) + r0 * 4, make_uint4(__float_as_uint(esn[0]), __float_as_uint(esn[1]),
-                                                 __float_as_uint(esn[2]), __float_as_uint(esn[3])));
-        if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_of(D_RSCALE), __float_as_uint(esn[0]));
+#define CARRY_SLOT_VEC_Q (sb + L::kQ)
+#define CARRY_SLOT_VEC_K (sb + L::kK)
+#define CARRY_SLOT_VEC_V (sb + L::kV)
+#define CARRY_SLOT_OUT(idx, value) store_from_float(p.out, (long long)out_row * kT + (idx), p.o_dtype, (value))
+#define CARRY_SLOT_PUT_SSCALE(r0_, v4_) stg_v4(dst_of(D_SSCALE) + (r0_) * 4, (v4_))
+#define CARRY_SLOT_PUT_CODES(r0_, c0_, cw_)                                                   \
+  {                                                                                           \
+    const unsigned long long base = dst_of(D_CODES) + (r0_) * kT + (c0_);                     \
+    stg_v4_at<0 * kT>(base, make_uint4(cw_[0][0], cw_[0][1], cw_[0][2], cw_[0][3]));          \
+    stg_v4_at<1 * kT>(base, make_uint4(cw_[1][0], cw_[1][1], cw_[1][2], cw_[1][3]));          \
+    stg_v4_at<2 * kT>(base, make_uint4(cw_[2][0], cw_[2][1], cw_[2][2], cw_[2][3]));          \
+    stg_v4_at<3 * kT>(base, make_uint4(cw_[3][0], cw_[3][1], cw_[3][2], cw_[3][3]));          \
+  }
+#define CARRY_SLOT_HEAD_RED head_red[grp][cnt & 1]
+#define CARRY_SLOT_MEET(statement)                \
+  if (lane == 0) { statement; claim_next(cnt); }  \
+  warps_meet(bar0 + 3);                           \
+  refill_stage(cnt, it);                          \
+  PROF_MARK(5)
+#define CARRY_SLOT_RESID_BEGIN() const unsigned long long dst_resid = dst_of(D_RESID)
+#define CARRY_SLOT_PUT_RESID4(i_, r0_, c0_, w_)                                    \
+  {                                                                                \
+    const unsigned long long base = dst_resid + (r0_) * (kT / 2) + (c0_) / 2;      \
+    if (i_ == 0) stg_v2_at<0 * (kT / 2)>(base, w_);                                \
+    if (i_ == 1) stg_v2_at<1 * (kT / 2)>(base, w_);                                \
+    if (i_ == 2) stg_v2_at<2 * (kT / 2)>(base, w_);                                \
+    if (i_ == 3) stg_v2_at<3 * (kT / 2)>(base, w_);                                \
+  }
+#define CARRY_SLOT_PUT_RESID8(i_, r0_, c0_, w_)                                    \
+  {                                                                                \
+    const unsigned long long base = dst_resid + (r0_) * kT + (c0_);                \
+    const uint4 pw = w_;                                                           \
+    if (i_ == 0) stg_v4_at<0 * kT>(base, pw);                                      \
+    if (i_ == 1) stg_v4_at<1 * kT>(base, pw);                                      \
+    if (i_ == 2) stg_v4_at<2 * kT>(base, pw);                                      \
+    if (i_ == 3) stg_v4_at<3 * kT>(base, pw);                                      \
+  }
+#define CARRY_SLOT_PUT_RSCALE_V(r0_, v4_) stg_v4(dst_of(D_RSCALE) + (r0_) * 4, (v4_))
+#define CARRY_SLOT_PUT_RSCALE_HEAD(bits_) stg_b32(dst_of(D_RSCALE), (bits_))
+#include "carry_gdn_slot_tile.inc"
+#undef CARRY_SLOT_VEC_Q
+#undef CARRY_SLOT_VEC_K
+#undef CARRY_SLOT_VEC_V
+#undef CARRY_SLOT_OUT
+#undef CARRY_SLOT_PUT_SSCALE
+#undef CARRY_SLOT_PUT_CODES
+#undef CARRY_SLOT_HEAD_RED
+#undef CARRY_SLOT_MEET
+#undef CARRY_SLOT_RESID_BEGIN
+#undef CARRY_SLOT_PUT_RESID4
+#undef CARRY_SLOT_PUT_RESID8
+#undef CARRY_SLOT_PUT_RSCALE_V
+#undef CARRY_SLOT_PUT_RSCALE_HEAD
       } else {
         // ---------------- statequant layout [K][V]: lane = 4 columns x 16 rows ----
         // columns {c0, c0+1} are held as pair A, {c0+2, c0+3} as pair B

@@ -41,23 +41,11 @@ RESID_INT4 = 1
 _RES_ID = {RESID_INT8: _lib.RES_INT8, RESID_INT4: _lib.RES_INT4}
 
 
-def quantized_gated_delta_rule_packed_decode(
-    mixed_qkv: torch.Tensor,
-    a: torch.Tensor,
-    b: torch.Tensor,
-    A_log: torch.Tensor,
-    dt_bias: torch.Tensor,
-    scale: float,
-    state_codes: torch.Tensor,
-    state_scale: torch.Tensor,
-    resid_codes: torch.Tensor,
-    resid_scale: torch.Tensor,
-    out: torch.Tensor,
-    ssm_state_indices: torch.Tensor,
-    use_qk_l2norm_in_kernel: bool = False,
-    resid_fmt: int = RESID_INT8,
-):
-    """Advance every request's slot by one token, in place; returns ``out``."""
+def _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scale, resid_codes, resid_scale,
+                 out, out_shape_of, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt):
+    """Validation shared by the single- and the multi-token call (the reference's conditions,
+    ``vllm_integration/quantized_packed_decode.py:268-307``) and the filled argument block.
+    ``mixed_qkv``, ``a``, ``b`` are the 2-D views of one token per request."""
     if mixed_qkv.dim() != 2:
         raise ValueError(f"mixed_qkv must be 2-D, got {tuple(mixed_qkv.shape)}")
     if mixed_qkv.stride(-1) != 1:
@@ -83,8 +71,9 @@ def quantized_gated_delta_rule_packed_decode(
 
     B = mixed_qkv.shape[0]
     num_slots, HV, V, K = state_codes.shape
-    if out.shape != (B, 1, HV, V):
-        raise ValueError(f"out must be {(B, 1, HV, V)}, got {tuple(out.shape)}")
+    want_out = out_shape_of(B, HV, V)
+    if tuple(out.shape) != want_out:
+        raise ValueError(f"out must be {want_out}, got {tuple(out.shape)}")
     if not out.is_contiguous():
         raise ValueError("out must be contiguous")
 
@@ -141,11 +130,88 @@ def quantized_gated_delta_rule_packed_decode(
     args.eps_mode = _lib.EPS_ON_SCALE
     args.qmax = QMAX_INT8
     args.status = None
+    return args, (A_log, dt_bias)       # the contiguous copies must outlive the launch call
+
+
+def quantized_gated_delta_rule_packed_decode(
+    mixed_qkv: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    A_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    scale: float,
+    state_codes: torch.Tensor,
+    state_scale: torch.Tensor,
+    resid_codes: torch.Tensor,
+    resid_scale: torch.Tensor,
+    out: torch.Tensor,
+    ssm_state_indices: torch.Tensor,
+    use_qk_l2norm_in_kernel: bool = False,
+    resid_fmt: int = RESID_INT8,
+):
+    """Advance every request's slot by one token, in place; returns ``out``."""
+    args, _keep = _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scale, resid_codes,
+                               resid_scale, out, lambda B, HV, V: (B, 1, HV, V), ssm_state_indices,
+                               use_qk_l2norm_in_kernel, resid_fmt)
     lib = _lib.load_library()
     dev = state_codes.device
     with torch.cuda.device(dev):
         rc = lib.carry_gdn_packed_decode(args, _lib.current_stream_ptr(dev))
     _lib.check(rc, "carry_gdn_packed_decode")
+    return out
+
+
+def quantized_gated_delta_rule_packed_decode_multi(
+    mixed_qkv: torch.Tensor,
+    a: torch.Tensor,
+    b: torch.Tensor,
+    A_log: torch.Tensor,
+    dt_bias: torch.Tensor,
+    scale: float,
+    state_codes: torch.Tensor,
+    state_scale: torch.Tensor,
+    resid_codes: torch.Tensor,
+    resid_scale: torch.Tensor,
+    out: torch.Tensor,
+    ssm_state_indices: torch.Tensor,
+    use_qk_l2norm_in_kernel: bool = False,
+    resid_fmt: int = RESID_INT8,
+):
+    """Advance every request's slot by T tokens in one call, in place; returns ``out``.
+
+    ``mixed_qkv`` is ``[B, T, 2*H*K + HV*V]``, ``a`` and ``b`` ``[B, T, HV]``, ``out``
+    ``[B, T, HV, V]``; everything else as in the single-token call.  The result is
+    that of T single-token calls on ``mixed_qkv[:, t]`` in turn, bit for bit; the
+    state tile of a request stays on chip between its tokens.  (No counterpart in
+    carrykernel: this is the multi-token decode vLLM reaches through its
+    speculative-decoding path.)"""
+    if mixed_qkv.dim() != 3 or a.dim() != 3 or b.dim() != 3:
+        raise ValueError("mixed_qkv, a and b must be 3-D: [B, T, ...]")
+    B, T = mixed_qkv.shape[0], mixed_qkv.shape[1]
+    if T < 1 or a.shape[:2] != (B, T) or b.shape[:2] != (B, T):
+        raise ValueError("mixed_qkv, a and b must agree on [B, T]")
+    step, _keep = _packed_args(mixed_qkv[:, 0], a[:, 0], b[:, 0], A_log, dt_bias, scale, state_codes, state_scale,
+                               resid_codes, resid_scale, out, lambda B_, HV, V: (B_, T, HV, V), ssm_state_indices,
+                               use_qk_l2norm_in_kernel, resid_fmt)
+    args = _lib.PackedMultiArgs()
+    args.step = step
+    args.T = T
+    args.stride_mixed_t, args.stride_a_t, args.stride_b_t = mixed_qkv.stride(1), a.stride(1), b.stride(1)
+    lib = _lib.load_library()
+    dev = state_codes.device
+    with torch.cuda.device(dev):
+        rc = lib.carry_gdn_packed_decode_multi(args, _lib.current_stream_ptr(dev))
+    if rc == _lib.ERR_UNSUPPORTED:
+        # shapes the streaming kernels do not take: one single-token call per token, each into a
+        # dense [B, 1, HV, V] block that is then copied into place
+        tmp = torch.empty((B, 1) + tuple(out.shape[2:]), dtype=out.dtype, device=out.device)
+        for t in range(T):
+            quantized_gated_delta_rule_packed_decode(
+                mixed_qkv[:, t], a[:, t], b[:, t], A_log, dt_bias, scale, state_codes, state_scale, resid_codes,
+                resid_scale, tmp, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt)
+            out[:, t:t + 1].copy_(tmp)
+        return out
+    _lib.check(rc, "carry_gdn_packed_decode_multi")
     return out
 
 

@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define CARRY_GDN_ABI_VERSION 1
+#define CARRY_GDN_ABI_VERSION 2
 
 /* element types of activations / outputs */
 enum { CARRY_F32 = 0, CARRY_BF16 = 1, CARRY_F16 = 2 };
@@ -164,6 +164,32 @@ typedef struct CarryGdnPackedArgs {
 
 int carry_gdn_packed_decode(const CarryGdnPackedArgs* args, void* stream);
 
+/*
+ * T consecutive tokens of every request in one call: the same step applied T
+ * times to each request's slot, with the slot's tile held on chip in between,
+ * so the state crosses HBM once per call instead of once per token.  Results
+ * are those of T calls of carry_gdn_packed_decode, bit for bit.  No such entry
+ * exists in the reference; it is the multi-token decode that vLLM reaches
+ * through its speculative-decoding path (the sibling of the call
+ * vllm_integration/quantized_packed_decode.py:242 mirrors).
+ *
+ * `step` describes token 0 exactly as for carry_gdn_packed_decode, with
+ * mixed_qkv [B, T, width], a and b [B, T, HV] and out [B, T, HV, V] contiguous:
+ * stride_*_tok are the strides between requests, stride_*_t those between the
+ * tokens of one request (in elements).  Only the shapes the streaming kernel
+ * takes are supported (K = V = 128, 16-byte aligned rows); anything else
+ * returns CARRY_GDN_ERR_UNSUPPORTED and the caller loops over tokens.
+ */
+typedef struct CarryGdnPackedMultiArgs {
+  CarryGdnPackedArgs step;
+  int32_t T;
+  int64_t stride_mixed_t;
+  int64_t stride_a_t;
+  int64_t stride_b_t;
+} CarryGdnPackedMultiArgs;
+
+int carry_gdn_packed_decode_multi(const CarryGdnPackedMultiArgs* args, void* stream);
+
 /* Human-readable text for a CARRY_GDN_ERR_* code (static storage). */
 const char* carry_gdn_strerror(int code);
 
@@ -172,7 +198,8 @@ int carry_gdn_abi_version(void);
 
 /*
  * Which kernel the last successful call on this host thread selected:
- * 0 = none yet, 1 = generic tile kernel, 2 = 128x128 streaming kernel.
+ * 0 = none yet, 1 = generic tile kernel, 2 = 128x128 streaming kernel,
+ * 3 = multi-token kernel.
  * Diagnostic only (tests use it to prove which path ran).
  */
 int carry_gdn_last_kernel(void);

@@ -43,12 +43,17 @@ def test_struct_sizes_match_header_layout():
     assert C.sizeof(_lib.StepArgs) == 14 * 8 + 11 * 4 + 4 + 8
     assert C.sizeof(_lib.Fp32Args) == 8 * 8 + 6 * 4
     assert C.sizeof(_lib.PackedArgs) % 8 == 0
+    assert C.sizeof(_lib.PackedMultiArgs) == C.sizeof(_lib.PackedArgs) + 8 + 3 * 8
 
 
 def test_argument_errors_return_codes_without_a_gpu(lib):
     assert lib.carry_gdn_quant_step(None, None) == -1
     assert lib.carry_gdn_fp32_step(None, None) == -1
     assert lib.carry_gdn_packed_decode(None, None) == -1
+    assert lib.carry_gdn_packed_decode_multi(None, None) == -1
+    m = _lib.PackedMultiArgs()
+    m.T = 0
+    assert lib.carry_gdn_packed_decode_multi(C.byref(m), None) == -2
     a = _lib.StepArgs()
     a.B, a.HV, a.K, a.V, a.qmax = 1, 1, 0, 128, 127.0
     assert lib.carry_gdn_quant_step(a, None) == -2          # K <= 0
