@@ -174,6 +174,14 @@ __device__ __forceinline__ float2 s8x2_to_float(uint32_t w) {
                                __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7440 | B)));
   return add2(m, splat(-kMagicByte));
 }
+// signed bytes A and B of w (as stored, no bias) -> floats, by the conversion instruction, which picks the
+// byte itself.  It runs on the quarter-rate conversion pipe, which has nothing else to do in these kernels:
+// against the byte-permute route (s8x2_to_float) it frees 1.25 ALU instructions and half a packed add per
+// element on the two pipes that bound the kernel.
+template <int A, int B>
+__device__ __forceinline__ float2 s8x2_cvt(uint32_t w) {
+  return make_float2((float)(signed char)((w >> (8 * A)) & 0xffu), (float)(signed char)((w >> (8 * B)) & 0xffu));
+}
 // bytes A and B of w (each nibble already XOR-ed with 8): {low nibbles}, {16 * high nibbles}
 template <int A, int B>
 __device__ __forceinline__ void s4x4_to_float(uint32_t w, float2& lo, float2& hi16) {
