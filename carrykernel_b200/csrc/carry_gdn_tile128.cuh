@@ -682,9 +682,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     }
   };
   auto refill_stage = [&](int cnt, int num) {
-#ifdef CARRY_EXP_NOREFILL
-    return;
-#endif
     if (gw == (cnt & (kWarps - 1)) && lane == 0 && num + S < my_tiles && !*poison) load_tile(num + S);
   };
 
@@ -710,11 +707,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const uint4 tm0 = lds_v4(tm);
     const int n = (int)tm0.x, hv = (int)(tm0.y & 0xffffu);
 
-#ifdef CARRY_EXP_NOREFILL
-    const bool healthy = (it >= S) ? true : mbar_wait(&full_bar[s], parity, poison, p.status);
-#else
     const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
-#endif
     PROF_MARK(0)
     const int slot = (int)tm0.z;
     const int out_row = n * p.HV + hv;                // outputs of this tile start at element out_row * 128
