@@ -796,13 +796,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         float* red_dot = col_red;                       // [warp][col][2]
         float* red_max = col_red + kWarps * kT * 2;     // [warp][col]
         float* red_emax = red_max + kWarps * kT;        // [warp][col]
-        float krow[16], qrow[16];            // k and q of this warp's 16 rows (the same in every lane)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float4 k4 = act4<QDT>(sb + L::kK, r0 + 4 * i), q4 = act4<QDT>(sb + L::kQ, r0 + 4 * i);
-          krow[4 * i] = k4.x * k_mul; krow[4 * i + 1] = k4.y * k_mul; krow[4 * i + 2] = k4.z * k_mul; krow[4 * i + 3] = k4.w * k_mul;
-          qrow[4 * i] = q4.x * q_mul; qrow[4 * i + 1] = q4.y * q_mul; qrow[4 * i + 2] = q4.z * q_mul; qrow[4 * i + 3] = q4.w * q_mul;
-        }
+        // k and q of this warp's 16 rows are the same in every lane; they are read from the stage where they
+        // are used (a broadcast load) instead of being held in 32 registers.  k_mul and q_mul are 1 in this
+        // layout's callers but are applied all the same.
+        auto k_of = [&](int i) { return act<QDT>(sb + L::kK, r0 + i) * k_mul; };
+        auto q_of = [&](int i) { return act<QDT>(sb + L::kQ, r0 + i) * q_mul; };
         float scol[4];
         {
           const float4 s4 = *reinterpret_cast<const float4*>(sscale + c0);
@@ -817,7 +815,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
           const float2 a = mul2(mul2(s8x2_to_float<0, 1>(w), sA), alpha2);
           const float2 b = mul2(mul2(s8x2_to_float<2, 3>(w), sB), alpha2);
           hA[i] = a; hB[i] = b;
-          const float2 kr = splat(krow[i]), qr = splat(qrow[i]);
+          const float2 kr = splat(k_of(i)), qr = splat(q_of(i));
           dkA = fma2(a, kr, dkA); dkB = fma2(b, kr, dkB);
           dqA = fma2(a, qr, dqA); dqB = fma2(b, qr, dqB);
         }
@@ -862,7 +860,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
             eA = mul2(s8x2_to_float<0, 1>(w), make_float2(es_col[0], es_col[1]));
             eB = mul2(s8x2_to_float<2, 3>(w), make_float2(es_col[2], es_col[3]));
           }
-          const float2 kr = splat(krow[i]);
+          const float2 kr = splat(k_of(i));
           const float2 tA = add2(fma2(kr, dvA, hA[i]), eA);
           const float2 tB = add2(fma2(kr, dvB, hB[i]), eB);
           hA[i] = tA; hB[i] = tB;
