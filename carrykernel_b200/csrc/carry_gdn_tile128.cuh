@@ -7,8 +7,8 @@
 //
 // One persistent CTA per SM walks its share of the tile list (tile = blockIdx.x +
 // number * gridDim.x) through a ring of stages: while tiles are computed, the loads
-// of the next ones are in flight.  The CTA holds two groups of 8 warps (one group
-// where a variant needs more than 128 registers per thread); each group works on a
+// of the next ones are in flight.  The CTA holds two groups of 8 warps (a single
+// group only if two stages per group did not fit); each group works on a
 // whole tile, and the groups take tiles off the CTA's list as they go, because the
 // two do not get equal shares of the SM's issue slots.  A stage is handed back
 // right after the tile's last meeting, when its last byte has been read, and
@@ -296,13 +296,13 @@ struct StageLayout {
   static constexpr int kV = kK + kVecBytes;
   static constexpr int kBytes = kV + kVecBytes;
   static_assert(kBytes % 128 == 0, "stages keep the ring's 128-byte alignment");
-  // Two groups of 8 warps share one CTA (and one SM) when a group's registers allow it -- at least 3
-  // stages per group must fit too -- else the CTA is a single group.
+  // Two groups of 8 warps share one CTA (and one SM) when at least 2 stages per group fit (every
+  // variant today; 128 registers per thread then), else the CTA is a single group.
 #ifdef CARRY_FORCE_1GROUP
   static constexpr int kGroups = 1;
 #else
   static constexpr int kGroups =
-      (LAYOUT == 1 && RES != CARRY_RES_INT4) ? 1 : ((6 * kBytes + 2 * kStaticOf(LAYOUT) <= kSmemPerCta) ? 2 : 1);
+      ((4 * kBytes + 2 * kStaticOf(LAYOUT) <= kSmemPerCta) ? 2 : 1);
 #endif
   static constexpr int kStatic = kGroups * kStaticOf(LAYOUT);
   static constexpr int kBudget = kSmemPerCta - kStatic;
