@@ -11,11 +11,14 @@ namespace {
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 }  // namespace
 
-// The streaming kernel needs K = V = 128, an integer residual, a per-V state
+// The streaming kernel needs K = V = 128, an integer residual (any residual format in the statequant
+// layout), a per-V state
 // scale, qmax = 2^(bits-1) - 1 for 3..8 bits, and 16-byte aligned, dense rows for every bulk copy.
 bool tile128_eligible(const KParams& p) {
   if (p.K != 128 || p.V != 128) return false;
-  if (p.res_fmt != CARRY_RES_INT8 && p.res_fmt != CARRY_RES_INT4) return false;
+  const bool int_resid = p.res_fmt == CARRY_RES_INT8 || p.res_fmt == CARRY_RES_INT4;
+  const bool float_resid = p.res_fmt == CARRY_RES_FP32 || p.res_fmt == CARRY_RES_FP16 || p.res_fmt == CARRY_RES_FP8;
+  if (!int_resid && !(float_resid && !p.packed)) return false;   // float residuals: statequant layout only
   if (p.sscale_mode != CARRY_SCALE_PER_V) return false;
   // the kernel divides by qmax with a multiply and a correcting fused multiply-add, which equals the
   // IEEE quotient for these values (the quantisation widths 3..8 bits) and has not been checked for others
@@ -24,7 +27,8 @@ bool tile128_eligible(const KParams& p) {
   if (p.HV > 128 || (long long)p.B * p.HV > 0x7fffffffLL) return false;
   const int qes = p.qkv_dtype == CARRY_F32 ? 4 : 2;
   if (!aligned16(p.codes_in) || !aligned16(p.codes_out) || !aligned16(p.resid_in) || !aligned16(p.resid_out) ||
-      !aligned16(p.sscale_in) || !aligned16(p.sscale_out) || !aligned16(p.rscale_in) || !aligned16(p.rscale_out) ||
+      !aligned16(p.sscale_in) || !aligned16(p.sscale_out) ||
+      (int_resid && (!aligned16(p.rscale_in) || !aligned16(p.rscale_out))) ||
       !aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.out))
     return false;
   if (p.packed) {
@@ -33,7 +37,7 @@ bool tile128_eligible(const KParams& p) {
     if (p.rscale_mode == CARRY_SCALE_PER_V ? (p.stride_rscale_slot % 4) : (p.stride_rscale_slot % 4 || p.HV % 4))
       return false;
   } else {
-    if (p.rscale_mode == CARRY_SCALE_PER_HEAD && p.HV % 4) return false;
+    if (int_resid && p.rscale_mode == CARRY_SCALE_PER_HEAD && p.HV % 4) return false;
   }
   return true;
 }

@@ -182,6 +182,19 @@ template <int A, int B>
 __device__ __forceinline__ float2 s8x2_cvt(uint32_t w) {
   return make_float2((float)(signed char)((w >> (8 * A)) & 0xffu), (float)(signed char)((w >> (8 * B)) & 0xffu));
 }
+// four fp8-e5m2 values in a word -> floats.  An e5m2 value is the upper byte of the half with the same
+// value, so each pair of bytes becomes a half2 by one byte permute.
+__device__ __forceinline__ void e5m2x4_to_float(uint32_t w, float2& ab, float2& cd) {
+  const uint32_t h01 = __byte_perm(w, 0u, 0x1404), h23 = __byte_perm(w, 0u, 0x3424);
+  ab = __half22float2(*reinterpret_cast<const __half2*>(&h01));
+  cd = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+}
+// ... and back, round to nearest even, saturating at the largest finite value
+__device__ __forceinline__ uint32_t float4_to_e5m2x4(float2 ab, float2 cd) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(ab, __NV_SATFINITE, __NV_E5M2);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(cd, __NV_SATFINITE, __NV_E5M2);
+  return lo | (hi << 16);
+}
 // bytes A and B of w (each nibble already XOR-ed with 8): {low nibbles}, {16 * high nibbles}
 template <int A, int B>
 __device__ __forceinline__ void s4x4_to_float(uint32_t w, float2& lo, float2& hi16) {
@@ -285,13 +298,17 @@ constexpr int kSmemPerCta = 231424;     // one CTA per SM: 227 KB less 1 KB
 template <int RES, int LAYOUT, int QDT, int RSCALE>
 struct StageLayout {
   static constexpr int kVecBytes = kT * (QDT == CARRY_F32 ? 4 : 2);
-  static constexpr int kResidBytes = (RES == CARRY_RES_INT4) ? kT * kT / 2 : kT * kT;
+  // integer residuals carry a scale (per V or per head); the float ones (fp32, fp16, fp8-e5m2) do not
+  static constexpr bool kFloatResid = RES == CARRY_RES_FP32 || RES == CARRY_RES_FP16 || RES == CARRY_RES_FP8;
+  static constexpr int kResidBytes = (RES == CARRY_RES_INT4) ? kT * kT / 2
+                                     : (RES == CARRY_RES_FP32) ? kT * kT * 4
+                                     : (RES == CARRY_RES_FP16) ? kT * kT * 2 : kT * kT;
   static constexpr int kCodes = 0;
   static constexpr int kResid = kT * kT;
   static constexpr int kSScale = kResid + kResidBytes;       // 128 floats
   static constexpr int kRScale = kSScale + 512;              // 128 floats (per V), or the 16 bytes that hold
-  static constexpr int kRScaleBytes = (RSCALE == CARRY_SCALE_PER_V) ? 512 : 16;   // this head's scale (per head)
-  static constexpr int kQ = kRScale + ((RSCALE == CARRY_SCALE_PER_V) ? 512 : 128);   // raw q, k, v of this head
+  static constexpr int kRScaleBytes = kFloatResid ? 0 : (RSCALE == CARRY_SCALE_PER_V) ? 512 : 16;   // this head's scale (per head)
+  static constexpr int kQ = kRScale + (kFloatResid ? 0 : (RSCALE == CARRY_SCALE_PER_V) ? 512 : 128);   // raw q, k, v of this head
   static constexpr int kK = kQ + kVecBytes;
   static constexpr int kV = kK + kVecBytes;
   static constexpr int kBytes = kV + kVecBytes;
@@ -420,7 +437,8 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
                                                unsigned long long (&a)[8]) {
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   constexpr long long KV = kT * kT;
-  constexpr long long RB = (RES == CARRY_RES_INT4) ? KV / 2 : KV;
+  constexpr long long RB = (RES == CARRY_RES_INT4) ? KV / 2 : (RES == CARRY_RES_FP32) ? 4 * KV
+                           : (RES == CARRY_RES_FP16) ? 2 * KV : KV;
   const long long nh = (long long)n * p.HV + hv;
   if (p.packed) {
     a[D_CODES] = reinterpret_cast<unsigned long long>(p.codes_out + slot * p.stride_state_slot + hv * KV);
@@ -537,7 +555,7 @@ __device__ __forceinline__ void issue_copies(const KParams& p, uint8_t* sb, uint
   bulk_load(sb + L::kCodes, reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT, bar);
   bulk_load(sb + L::kResid, reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes, bar);
   bulk_load(sb + L::kSScale, reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512, bar);
-  bulk_load(sb + L::kRScale, reinterpret_cast<const void*>(a[D_RSCALE_IN]), rscale_bytes, bar);
+  if constexpr (rscale_bytes > 0) bulk_load(sb + L::kRScale, reinterpret_cast<const void*>(a[D_RSCALE_IN]), rscale_bytes, bar);
   bulk_load(sb + L::kQ, reinterpret_cast<const void*>(a[D_Q]), L::kVecBytes, bar);
   bulk_load(sb + L::kK, reinterpret_cast<const void*>(a[D_K]), L::kVecBytes, bar);
   bulk_load(sb + L::kV, reinterpret_cast<const void*>(a[D_V]), L::kVecBytes, bar);
@@ -841,14 +859,23 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         for (int b = 0; b < 4; ++b) {
           dv[b] = __fmul_rn(beta, __fadd_rn(act<QDT>(sb + L::kV, c0 + b), -dk[b]));
           oval[b] = fmaf(dv[b], kq, dq[b]);
-          es_col[b] = (RSCALE == CARRY_SCALE_PER_V) ? rscale[c0 + b] : es_head;
+          es_col[b] = L::kFloatResid ? 0.f : (RSCALE == CARRY_SCALE_PER_V) ? rscale[c0 + b] : es_head;
         }
         const float2 dvA = make_float2(dv[0], dv[1]), dvB = make_float2(dv[2], dv[3]);
         float amax[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
           float2 eA, eB;
-          if constexpr (RES == CARRY_RES_INT4) {
+          if constexpr (RES == CARRY_RES_FP32) {
+            const float4 e4 = *reinterpret_cast<const float4*>(sb + L::kResid + ((r0 + i) * kT + c0) * 4);
+            eA = make_float2(e4.x, e4.y); eB = make_float2(e4.z, e4.w);
+          } else if constexpr (RES == CARRY_RES_FP16) {
+            const uint2 e2 = *reinterpret_cast<const uint2*>(sb + L::kResid + ((r0 + i) * kT + c0) * 2);
+            eA = __half22float2(*reinterpret_cast<const __half2*>(&e2.x));
+            eB = __half22float2(*reinterpret_cast<const __half2*>(&e2.y));
+          } else if constexpr (RES == CARRY_RES_FP8) {
+            e5m2x4_to_float(*reinterpret_cast<const uint32_t*>(sb + L::kResid + (r0 + i) * kT + c0), eA, eB);
+          } else if constexpr (RES == CARRY_RES_INT4) {
             const uint32_t w =
                 (uint32_t)(*reinterpret_cast<const uint16_t*>(sb + L::kResid + (r0 + i) * (kT / 2) + c0 / 2)) ^ 0x8888u;
             float2 lo, hi;                              // lo = cols {c0, c0+2}, hi = 16 * cols {c0+1, c0+3}
@@ -914,6 +941,30 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) stg_b32(dst_codes + (r0 + i) * kT + c0, cw[i]);
         }
+        if constexpr (L::kFloatResid) {
+          // the new residual is stored as it is, in its format; the meeting only hands the stage on
+          if (lane == 0) claim_next(cnt);
+          warps_meet(bar0 + 3);
+          refill_stage(cnt, it);
+          const unsigned long long dst_resid = dst_of(D_RESID);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            if constexpr (RES == CARRY_RES_FP32) {
+              stg_v4(dst_resid + ((r0 + i) * kT + c0) * 4,
+                     make_uint4(__float_as_uint(hA[i].x), __float_as_uint(hA[i].y), __float_as_uint(hB[i].x),
+                                __float_as_uint(hB[i].y)));
+            } else if constexpr (RES == CARRY_RES_FP16) {
+              const __half2 a2 = __floats2half2_rn(hA[i].x, hA[i].y), b2 = __floats2half2_rn(hB[i].x, hB[i].y);
+              stg_v2_at<0>(dst_resid + ((r0 + i) * kT + c0) * 2,
+                           make_uint2(*reinterpret_cast<const uint32_t*>(&a2), *reinterpret_cast<const uint32_t*>(&b2)));
+            } else {
+              stg_b32(dst_resid + (r0 + i) * kT + c0, float4_to_e5m2x4(hA[i], hB[i]));
+            }
+          }
+          if ((lane >> 2) == gw)
+            stg_v4(dst_of(D_SSCALE) + c0 * 4, make_uint4(__float_as_uint(snew[0]), __float_as_uint(snew[1]),
+                                                         __float_as_uint(snew[2]), __float_as_uint(snew[3])));
+        } else {
         float esn[4];
         if constexpr (RSCALE == CARRY_SCALE_PER_V) {
           *reinterpret_cast<float4*>(red_emax + (size_t)gw * kT + c0) =
@@ -964,6 +1015,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
                                                    __float_as_uint(esn[2]), __float_as_uint(esn[3])));
         }
         if (RSCALE == CARRY_SCALE_PER_HEAD && gtid == 0) stg_b32(dst_of(D_RSCALE), __float_as_uint(esn[0]));
+        }
       }
     }
     PROF_MARK(6)
@@ -1040,6 +1092,11 @@ int launch_dtype(const KParams& p, cudaStream_t stream, int sms) {
 // all variants of one memory layout
 template <int LAYOUT>
 int launch_layout(const KParams& p, cudaStream_t stream, int sms) {
+  if constexpr (LAYOUT == LAYOUT_KV) {     // the float residual formats exist on the statequant surfaces only
+    if (p.res_fmt == CARRY_RES_FP32) return launch_dtype<LAYOUT, CARRY_RES_FP32, CARRY_SCALE_PER_V>(p, stream, sms);
+    if (p.res_fmt == CARRY_RES_FP16) return launch_dtype<LAYOUT, CARRY_RES_FP16, CARRY_SCALE_PER_V>(p, stream, sms);
+    if (p.res_fmt == CARRY_RES_FP8) return launch_dtype<LAYOUT, CARRY_RES_FP8, CARRY_SCALE_PER_V>(p, stream, sms);
+  }
   const bool i4 = p.res_fmt == CARRY_RES_INT4, pv = p.rscale_mode == CARRY_SCALE_PER_V;
   if (i4) return pv ? launch_dtype<LAYOUT, CARRY_RES_INT4, CARRY_SCALE_PER_V>(p, stream, sms)
                     : launch_dtype<LAYOUT, CARRY_RES_INT4, CARRY_SCALE_PER_HEAD>(p, stream, sms);
