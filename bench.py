@@ -61,7 +61,7 @@ assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
 # kernel on this workload (64 requests), from the ncu capture summarised under
 # profiles/gdn_tile128_int4_perhead_bf16_b64.md (mean of six steady-state launches, ncu with
 # --cache-control none so that the write-back of the results is inside the window).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 103_190_000
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 103_320_000
 
 
 def parse_args():
