@@ -14,7 +14,7 @@ import torch
 
 PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libcarry_gdn.so")
-ABI_VERSION = 2
+ABI_VERSION = 3
 
 F32, BF16, F16 = 0, 1, 2
 RES_FP32, RES_FP16, RES_FP8, RES_INT8, RES_INT4, RES_NONE = 0, 1, 2, 3, 4, 5
@@ -79,10 +79,47 @@ class PackedMultiArgs(C.Structure):
     ]
 
 
+class Pool(C.Structure):
+    _fields_ = [
+        ("state_codes", C.c_void_p), ("state_scale", C.c_void_p),
+        ("resid_codes", C.c_void_p), ("resid_scale", C.c_void_p),
+        ("stride_state_slot", C.c_int64), ("stride_resid_slot", C.c_int64),
+        ("stride_sscale_slot", C.c_int64), ("stride_rscale_slot", C.c_int64),
+        ("num_slots", C.c_int32), ("HV", C.c_int32), ("V", C.c_int32), ("K", C.c_int32),
+        ("res_fmt", C.c_int32), ("resid_scale_mode", C.c_int32),
+    ]
+
+
+class PoolStoreArgs(C.Structure):
+    _fields_ = [
+        ("pool", Pool), ("h", C.c_void_p), ("stride_h_req", C.c_int64), ("h_dtype", C.c_int32),
+        ("slots", C.c_void_p), ("stride_slots", C.c_int64), ("B", C.c_int32),
+        ("keep_error", C.c_int32), ("qmax", C.c_float), ("status", C.c_void_p),
+    ]
+
+
+class PoolLoadArgs(C.Structure):
+    _fields_ = [
+        ("pool", Pool), ("h", C.c_void_p), ("stride_h_req", C.c_int64), ("h_dtype", C.c_int32),
+        ("slots", C.c_void_p), ("stride_slots", C.c_int64), ("B", C.c_int32),
+        ("with_residual", C.c_int32), ("status", C.c_void_p),
+    ]
+
+
+class PoolCopyArgs(C.Structure):
+    _fields_ = [
+        ("src", Pool), ("dst", Pool),
+        ("src_slots", C.c_void_p), ("stride_src_slots", C.c_int64),
+        ("dst_slots", C.c_void_p), ("stride_dst_slots", C.c_int64),
+        ("B", C.c_int32), ("status", C.c_void_p),
+    ]
+
+
 ERR_UNSUPPORTED = -5
 
 EXPORTS = ("carry_gdn_quant_step", "carry_gdn_fp32_step", "carry_gdn_packed_decode",
-           "carry_gdn_packed_decode_multi", "carry_gdn_strerror", "carry_gdn_abi_version",
+           "carry_gdn_packed_decode_multi", "carry_gdn_pool_store", "carry_gdn_pool_load",
+           "carry_gdn_pool_copy", "carry_gdn_strerror", "carry_gdn_abi_version",
            "carry_gdn_last_kernel")
 
 _lib = None
@@ -116,8 +153,12 @@ def load_library(path: str | None = None):
         lib.carry_gdn_fp32_step.argtypes = [C.POINTER(Fp32Args), C.c_void_p]
         lib.carry_gdn_packed_decode.argtypes = [C.POINTER(PackedArgs), C.c_void_p]
         lib.carry_gdn_packed_decode_multi.argtypes = [C.POINTER(PackedMultiArgs), C.c_void_p]
+        lib.carry_gdn_pool_store.argtypes = [C.POINTER(PoolStoreArgs), C.c_void_p]
+        lib.carry_gdn_pool_load.argtypes = [C.POINTER(PoolLoadArgs), C.c_void_p]
+        lib.carry_gdn_pool_copy.argtypes = [C.POINTER(PoolCopyArgs), C.c_void_p]
         for fn in (lib.carry_gdn_quant_step, lib.carry_gdn_fp32_step, lib.carry_gdn_packed_decode,
-                   lib.carry_gdn_packed_decode_multi):
+                   lib.carry_gdn_packed_decode_multi, lib.carry_gdn_pool_store, lib.carry_gdn_pool_load,
+                   lib.carry_gdn_pool_copy):
             fn.restype = C.c_int
         if lib.carry_gdn_abi_version() != ABI_VERSION:
             raise CudaUnavailable(

@@ -166,4 +166,61 @@ int carry_gdn_packed_decode_multi(const CarryGdnPackedMultiArgs* m, void* stream
   return rc2;
 }
 
+namespace {
+int pool_ok(const CarryGdnPool& pool) {
+  if (pool.HV <= 0 || pool.K <= 0 || pool.V <= 0 || pool.num_slots < 0) return CARRY_GDN_ERR_SHAPE;
+  if (pool.res_fmt != CARRY_RES_INT8 && pool.res_fmt != CARRY_RES_INT4) return CARRY_GDN_ERR_FORMAT;
+  if (!scale_mode_ok(pool.resid_scale_mode)) return CARRY_GDN_ERR_FORMAT;
+  if (pool.res_fmt == CARRY_RES_INT4 && (pool.K & 1)) return CARRY_GDN_ERR_FORMAT;
+  return CARRY_GDN_OK;
+}
+bool pool_has_pointers(const CarryGdnPool& pool) {
+  return pool.state_codes && pool.state_scale && pool.resid_codes && pool.resid_scale;
+}
+}  // namespace
+
+int carry_gdn_pool_store(const CarryGdnPoolStoreArgs* a, void* stream) {
+  if (!a) return CARRY_GDN_ERR_NULL;
+  if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
+  const int rc = pool_ok(a->pool);
+  if (rc != CARRY_GDN_OK) return rc;
+  if (!(a->qmax >= 1.0f && a->qmax <= 127.0f)) return CARRY_GDN_ERR_SHAPE;
+  if (!dtype_ok(a->h_dtype)) return CARRY_GDN_ERR_DTYPE;
+  if (a->B == 0) return CARRY_GDN_OK;
+  if (!a->h || !a->slots || !pool_has_pointers(a->pool)) return CARRY_GDN_ERR_NULL;
+  const int rc2 = carry::launch_pool_store(*a, static_cast<cudaStream_t>(stream));
+  if (rc2 == CARRY_GDN_OK) g_last_kernel = 4;
+  return rc2;
+}
+
+int carry_gdn_pool_load(const CarryGdnPoolLoadArgs* a, void* stream) {
+  if (!a) return CARRY_GDN_ERR_NULL;
+  if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
+  const int rc = pool_ok(a->pool);
+  if (rc != CARRY_GDN_OK) return rc;
+  if (!dtype_ok(a->h_dtype)) return CARRY_GDN_ERR_DTYPE;
+  if (a->B == 0) return CARRY_GDN_OK;
+  if (!a->h || !a->slots || !pool_has_pointers(a->pool)) return CARRY_GDN_ERR_NULL;
+  const int rc2 = carry::launch_pool_load(*a, static_cast<cudaStream_t>(stream));
+  if (rc2 == CARRY_GDN_OK) g_last_kernel = 4;
+  return rc2;
+}
+
+int carry_gdn_pool_copy(const CarryGdnPoolCopyArgs* a, void* stream) {
+  if (!a) return CARRY_GDN_ERR_NULL;
+  if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
+  int rc = pool_ok(a->src);
+  if (rc == CARRY_GDN_OK) rc = pool_ok(a->dst);
+  if (rc != CARRY_GDN_OK) return rc;
+  if (a->src.HV != a->dst.HV || a->src.K != a->dst.K || a->src.V != a->dst.V) return CARRY_GDN_ERR_SHAPE;
+  if (a->src.res_fmt != a->dst.res_fmt || a->src.resid_scale_mode != a->dst.resid_scale_mode)
+    return CARRY_GDN_ERR_FORMAT;
+  if (a->B == 0) return CARRY_GDN_OK;
+  if (!a->src_slots || !a->dst_slots || !pool_has_pointers(a->src) || !pool_has_pointers(a->dst))
+    return CARRY_GDN_ERR_NULL;
+  const int rc2 = carry::launch_pool_copy(*a, static_cast<cudaStream_t>(stream));
+  if (rc2 == CARRY_GDN_OK) g_last_kernel = 4;
+  return rc2;
+}
+
 }  // extern "C"

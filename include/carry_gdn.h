@@ -22,7 +22,7 @@
 extern "C" {
 #endif
 
-#define CARRY_GDN_ABI_VERSION 2
+#define CARRY_GDN_ABI_VERSION 3
 
 /* element types of activations / outputs */
 enum { CARRY_F32 = 0, CARRY_BF16 = 1, CARRY_F16 = 2 };
@@ -190,6 +190,98 @@ typedef struct CarryGdnPackedMultiArgs {
 
 int carry_gdn_packed_decode_multi(const CarryGdnPackedMultiArgs* args, void* stream);
 
+/*
+ * The slot pool of one layer -- the four tensors carry_gdn_packed_decode
+ * updates -- for the calls that move a request's state in and out of it.  The
+ * reference keeps the pool as four torch tensors and seeds it with eager ops
+ * (init_quantized_state, vllm_integration/quantized_packed_decode.py:330-352);
+ * it names what a serving engine additionally needs of it -- the residual has
+ * to survive paging, preemption, prefix-cache reuse and speculative-decode
+ * rollback -- as work not done (same file :50-54).  Within a slot the tensors
+ * are contiguous [HV, V, K]; strides between slots are in elements.
+ */
+typedef struct CarryGdnPool {
+  int8_t* state_codes;    /* [slots, HV, V, K] */
+  float* state_scale;     /* [slots, HV, V] */
+  int8_t* resid_codes;    /* [slots, HV, V, K] (INT8) or [slots, HV, V, K/2] (INT4) */
+  float* resid_scale;     /* [slots, HV, V] (PER_V) or [slots, HV] (PER_HEAD) */
+  int64_t stride_state_slot;
+  int64_t stride_resid_slot;
+  int64_t stride_sscale_slot;
+  int64_t stride_rscale_slot;
+  int32_t num_slots, HV, V, K;
+  int32_t res_fmt;          /* CARRY_RES_INT8 | CARRY_RES_INT4 */
+  int32_t resid_scale_mode; /* CARRY_SCALE_* */
+} CarryGdnPool;
+
+/*
+ * Prefill hand-off: quantise the floating-point state h[n] ([HV, V, K], K
+ * contiguous -- the final state a prefill kernel returns) of request n into
+ * slot slots[n].  State codes and scales are those of init_quantized_state
+ * (quantized_packed_decode.py:346-350): scale = max(amax_K|h|, 1e-12) / qmax,
+ * codes = round_half_even(h / scale).  keep_error == 0 zeroes the slot's
+ * residual, as the reference does; keep_error != 0 stores the quantisation
+ * error h - codes * scale as the residual instead (encoded like a decode step
+ * encodes it), so the first decode step already feeds it back.  A slot id <= 0
+ * is padding and skipped.  Two requests must not name the same slot.
+ */
+typedef struct CarryGdnPoolStoreArgs {
+  CarryGdnPool pool;
+  const void* h;          /* [B, HV, V, K] */
+  int64_t stride_h_req;   /* elements between requests */
+  int32_t h_dtype;        /* CARRY_F32 | CARRY_BF16 | CARRY_F16 */
+  const int32_t* slots;   /* [B] */
+  int64_t stride_slots;
+  int32_t B;
+  int32_t keep_error;
+  float qmax;             /* state grid, 127 for 8 bits */
+  int32_t* status;        /* optional device word, may be NULL */
+} CarryGdnPoolStoreArgs;
+
+int carry_gdn_pool_store(const CarryGdnPoolStoreArgs* args, void* stream);
+
+/*
+ * The reverse: h[n] = codes * scale (+ resid_codes * resid_scale when
+ * with_residual != 0, which is the state the next decode step re-quantises)
+ * for slot slots[n], each product rounded to fp32 before the sum.  Hands a
+ * request back to a kernel that wants a floating-point state (a further prefill
+ * chunk, a swap-out in an engine's own format).  A slot id <= 0 writes zeros.
+ */
+typedef struct CarryGdnPoolLoadArgs {
+  CarryGdnPool pool;      /* read only */
+  void* h;                /* [B, HV, V, K] */
+  int64_t stride_h_req;
+  int32_t h_dtype;
+  const int32_t* slots;   /* [B] */
+  int64_t stride_slots;
+  int32_t B;
+  int32_t with_residual;
+  int32_t* status;
+} CarryGdnPoolLoadArgs;
+
+int carry_gdn_pool_load(const CarryGdnPoolLoadArgs* args, void* stream);
+
+/*
+ * Copy whole slots, residual included, bit for bit: slot src_slots[n] of `src`
+ * to slot dst_slots[n] of `dst` (the same pool, or a second pool of the same
+ * shape and formats: a spill pool for preempted requests, a checkpoint before
+ * speculative tokens, a prefix-cache entry).  Pairs with either id <= 0 are
+ * skipped.  No destination slot may be the source or destination of another
+ * pair of the same call.
+ */
+typedef struct CarryGdnPoolCopyArgs {
+  CarryGdnPool src;       /* read only */
+  CarryGdnPool dst;
+  const int32_t* src_slots; /* [B] */
+  int64_t stride_src_slots;
+  const int32_t* dst_slots; /* [B] */
+  int64_t stride_dst_slots;
+  int32_t B;
+  int32_t* status;
+} CarryGdnPoolCopyArgs;
+
+int carry_gdn_pool_copy(const CarryGdnPoolCopyArgs* args, void* stream);
+
 /* Human-readable text for a CARRY_GDN_ERR_* code (static storage). */
 const char* carry_gdn_strerror(int code);
 
@@ -199,7 +291,7 @@ int carry_gdn_abi_version(void);
 /*
  * Which kernel the last successful call on this host thread selected:
  * 0 = none yet, 1 = generic tile kernel, 2 = 128x128 streaming kernel,
- * 3 = multi-token kernel.
+ * 3 = multi-token kernel, 4 = a pool store / load / copy kernel.
  * Diagnostic only (tests use it to prove which path ran).
  */
 int carry_gdn_last_kernel(void);

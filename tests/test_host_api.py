@@ -44,6 +44,10 @@ def test_struct_sizes_match_header_layout():
     assert C.sizeof(_lib.Fp32Args) == 8 * 8 + 6 * 4
     assert C.sizeof(_lib.PackedArgs) % 8 == 0
     assert C.sizeof(_lib.PackedMultiArgs) == C.sizeof(_lib.PackedArgs) + 8 + 3 * 8
+    assert C.sizeof(_lib.Pool) == 4 * 8 + 4 * 8 + 6 * 4
+    assert C.sizeof(_lib.PoolStoreArgs) == C.sizeof(_lib.Pool) + 8 + 8 + 8 + 8 + 8 + 4 * 4 + 8
+    assert C.sizeof(_lib.PoolLoadArgs) == C.sizeof(_lib.Pool) + 8 + 8 + 8 + 8 + 8 + 2 * 4 + 8
+    assert C.sizeof(_lib.PoolCopyArgs) == 2 * C.sizeof(_lib.Pool) + 4 * 8 + 8 + 8
 
 
 def test_argument_errors_return_codes_without_a_gpu(lib):
@@ -76,6 +80,30 @@ def test_argument_errors_return_codes_without_a_gpu(lib):
     p.H = 2
     p.res_fmt = _lib.RES_FP32
     assert lib.carry_gdn_packed_decode(p, None) == -4       # slot path is int8/int4 only
+    for fn in (lib.carry_gdn_pool_store, lib.carry_gdn_pool_load, lib.carry_gdn_pool_copy):
+        assert fn(None, None) == -1
+    st = _lib.PoolStoreArgs()
+    st.B, st.qmax = 1, 127.0
+    assert lib.carry_gdn_pool_store(st, None) == -2         # empty head shape
+    st.pool.HV, st.pool.V, st.pool.K = 2, 4, 7
+    st.pool.res_fmt = _lib.RES_FP16
+    assert lib.carry_gdn_pool_store(st, None) == -4         # the pool holds int8 / int4 residuals only
+    st.pool.res_fmt = _lib.RES_INT4
+    assert lib.carry_gdn_pool_store(st, None) == -4         # int4 needs an even K
+    st.pool.K = 8
+    st.h_dtype = 7
+    assert lib.carry_gdn_pool_store(st, None) == -3
+    st.h_dtype = 0
+    assert lib.carry_gdn_pool_store(st, None) == -1         # pointers missing
+    st.B = 0
+    assert lib.carry_gdn_pool_store(st, None) == 0
+    cp = _lib.PoolCopyArgs()
+    cp.B = 1
+    cp.src.HV, cp.src.V, cp.src.K, cp.src.res_fmt = 2, 4, 8, _lib.RES_INT8
+    cp.dst.HV, cp.dst.V, cp.dst.K, cp.dst.res_fmt = 2, 4, 16, _lib.RES_INT8
+    assert lib.carry_gdn_pool_copy(cp, None) == -2          # head shapes differ
+    cp.dst.K, cp.dst.res_fmt = 8, _lib.RES_INT4
+    assert lib.carry_gdn_pool_copy(cp, None) == -4          # residual formats differ
     assert b"NULL" in lib.carry_gdn_strerror(-1)
     assert lib.carry_gdn_strerror(-99) == b"unknown error code"
 
@@ -115,6 +143,45 @@ def test_no_cpu_path():
     if not torch.cuda.is_available():
         with pytest.raises(binding.CudaUnavailable):
             binding.load_extension()
+
+
+def test_state_pool_validation_messages():
+    from carrykernel_b200.vllm_integration import state_pool as sp
+    pool = qpd.init_quantized_state(3, 2, 4, 8, "cpu", resid_fmt=qpd.RESID_INT4)
+    idx = torch.tensor([1], dtype=torch.int32)
+    h = torch.zeros(1, 2, 4, 8)
+    with pytest.raises(ValueError, match="packed two codes per byte"):
+        sp.store_state(h, (pool[0], pool[1], pool[0], pool[3]), idx, resid_fmt=qpd.RESID_INT4)
+    with pytest.raises(ValueError, match="same shape as the state"):
+        sp.store_state(h, pool, idx, resid_fmt=qpd.RESID_INT8)
+    with pytest.raises(ValueError, match="unknown residual format"):
+        sp.load_state(pool, idx, resid_fmt=9)
+    with pytest.raises(sp._lib.CudaUnavailable):             # no CPU path
+        sp.store_state(h, pool, idx, resid_fmt=qpd.RESID_INT4)
+
+
+def test_pool_oracle_round_trip():
+    """store -> load on the CPU oracle: the kept error brings the state back to
+    within half a residual step; copy moves all four tensors."""
+    g = torch.Generator().manual_seed(2)
+    h = torch.randn(2, 2, 6, 16, generator=g)
+    idx = torch.tensor([2, 1], dtype=torch.int32)
+    for fmt, rscale in ((orc.RESID_INT8, "v"), (orc.RESID_INT4, "head")):
+        pool = list(orc.init_quantized_pool(4, 2, 6, 16, resid_fmt=fmt, resid_scale=rscale))
+        orc.pool_store(h, *pool, idx, resid_fmt=fmt, keep_error=False)
+        ref = orc.init_quantized_pool(4, 2, 6, 16, h0=torch.cat([h[:1] * 0, h[1:2], h[0:1], h[:1] * 0]),
+                                      resid_fmt=fmt, resid_scale=rscale)
+        for a, b in zip(pool, ref):
+            assert torch.equal(a[1:3], b[1:3])
+        orc.pool_store(h, *pool, idx, resid_fmt=fmt, keep_error=True)
+        back = orc.pool_load(*pool, idx, resid_fmt=fmt)
+        rs = pool[3][idx.long()]
+        step = rs[..., None, None] if rscale == "head" else rs[..., None]
+        assert bool(((back - h).abs() <= 0.5 * step * (1 + 1e-5) + 1e-9).all())
+        spill = [torch.zeros_like(t[:2]) for t in pool]
+        orc.pool_copy(pool, spill, torch.tensor([2]), torch.tensor([1]))
+        for a, b in zip(pool, spill):
+            assert torch.equal(a[2], b[1]) and not b[0].any()
 
 
 def test_init_matches_oracle():
