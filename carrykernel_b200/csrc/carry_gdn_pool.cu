@@ -1,9 +1,11 @@
 // Moving a request's state in and out of the slot pool [slots, HV, V, K]:
 // quantise a floating-point state into a slot (prefill hand-off), dequantise a
-// slot back, and copy whole slots.  All three are plain streaming kernels: one
-// CTA works through (request, head) tiles, one warp per V-row, each lane on
-// VEC consecutive K elements, every row read from DRAM once (the second and
-// third look at a row hit L1).
+// slot back, and copy whole slots.  All three are plain streaming kernels: a
+// CTA works through (request, head) tiles, a warp on four V-rows at a time, a
+// lane on VEC consecutive K elements of each.  Rows of K = 32 * VEC elements
+// stay in registers between the row maximum and the encoding; other shapes go
+// through predicated loops that look at a row two or three times (once from
+// DRAM, then from L1).  The tile after the current one is asked into the L2.
 #include "carry_gdn_common.cuh"
 
 namespace carry {
