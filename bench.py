@@ -416,6 +416,19 @@ def run_reference_arm(args, rank):
     }))
 
 
+def l2_statement(args, batch, layers):
+    """Whether a step's working set exceeds the 126 MB L2 (the slots a step touches are the same
+    every step, so a small enough set stays cached between steps)."""
+    slot = HV * (K * V + (K * V // 2 if args.resid == "int4" else K * V) + V * 4 + 4)
+    per_layer, step = batch * slot / 1e6, batch * layers * slot / 1e6
+    if step > 2 * 126:
+        return (f"inputs larger than L2: each step touches a different {per_layer:.0f} MB of state per layer, "
+                f"{step / 1e3:.2f} GB per step against 126 MB of L2")
+    kind = "L2-RESIDENT" if step < 0.8 * 126 else "PARTLY L2-RESIDENT"
+    return (f"{kind}: a step's state is {step:.1f} MB ({per_layer:.1f} MB per layer) against 126 MB of L2; "
+            "not an HBM figure")
+
+
 def workload_config(args, batch, layers, note=None):
     cfg = {"workload": "slot-indexed GDN decode step: int8 state + packed int4 residual (per-head "
                        "residual scale), 24 layers x 64 requests per GPU, pools of 256 slots"
@@ -426,8 +439,7 @@ def workload_config(args, batch, layers, note=None):
            "pool_slots": POOL_SLOTS, "resid": args.resid,
            "resid_scale": "per-head" if args.resid_scale == "head" else "per-V",
            "activations": "bf16", "parallelism": f"slot-sharded x{args.gpus}, no collective",
-           "l2": "inputs larger than L2: each step touches a different 52 MB of state per layer, "
-                 "1.26 GB per step against 126 MB of L2"}
+           "l2": l2_statement(args, batch, layers)}
     if note:
         cfg["sample"] = note
     return cfg
