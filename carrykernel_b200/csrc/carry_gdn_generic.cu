@@ -239,6 +239,73 @@ __global__ void __launch_bounds__(kThreads) gdn_fp32_kernel(const __grid_constan
   for (int idx = tid; idx < K * V; idx += kThreads) hout[idx] = T[idx];
 }
 
+// The same step for K = V = 128 as a streaming kernel: the tile never sits in shared memory.
+// A CTA of 8 warps takes one (request, head) tile; a lane holds 4 consecutive columns of 16
+// rows (rows warp, warp + 8, ...: 64 state values in registers, 16 independent 16-byte reads
+// in flight per thread).  The two sums over K -- (alpha h)^T k and h'^T q -- are finished
+// across the warps through 4 KB of shared memory.  Each state element is read once and
+// written once; h_out may alias h_in (a thread reads its elements before it writes them).
+constexpr int kF = 128;
+__global__ void __launch_bounds__(kThreads, 2) gdn_fp32_tile128_kernel(const __grid_constant__ CarryGdnFp32Args a) {
+  __shared__ __align__(16) float red[kThreads / 32][kF];
+  __shared__ __align__(16) float sk[kF], sq[kF], sdv[kF];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, c0 = 4 * lane;
+  const long long tiles = (long long)a.B * a.HV;
+  for (long long nh = blockIdx.x; nh < tiles; nh += gridDim.x) {
+    const float* hin = a.h_in + nh * kF * kF;
+    float* hout = a.h_out + nh * kF * kF;
+    float4 h[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) h[j] = *reinterpret_cast<const float4*>(hin + (warp + 8 * j) * kF + c0);
+    if (tid < kF) {
+      sk[tid] = load_as_float(a.k, nh * kF + tid, a.qkv_dtype);
+      sq[tid] = load_as_float(a.q, nh * kF + tid, a.qkv_dtype);
+    }
+    const float alpha = a.alpha[nh], beta = a.beta[nh];
+    __syncthreads();
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float kk = sk[warp + 8 * j];
+      h[j].x = __fmul_rn(alpha, h[j].x); h[j].y = __fmul_rn(alpha, h[j].y);
+      h[j].z = __fmul_rn(alpha, h[j].z); h[j].w = __fmul_rn(alpha, h[j].w);
+      acc.x = fmaf(h[j].x, kk, acc.x); acc.y = fmaf(h[j].y, kk, acc.y);
+      acc.z = fmaf(h[j].z, kk, acc.z); acc.w = fmaf(h[j].w, kk, acc.w);
+    }
+    *reinterpret_cast<float4*>(&red[warp][c0]) = acc;
+    __syncthreads();
+    if (tid < kF) {
+      float read = red[0][tid];
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) read += red[w][tid];
+      sdv[tid] = __fmul_rn(beta, __fadd_rn(load_as_float(a.v, nh * kF + tid, a.qkv_dtype), -read));
+    }
+    __syncthreads();
+    const float4 dv = *reinterpret_cast<const float4*>(&sdv[c0]);
+    acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int row = warp + 8 * j;
+      const float kk = sk[row], qq = sq[row];
+      h[j].x = __fadd_rn(h[j].x, __fmul_rn(kk, dv.x)); h[j].y = __fadd_rn(h[j].y, __fmul_rn(kk, dv.y));
+      h[j].z = __fadd_rn(h[j].z, __fmul_rn(kk, dv.z)); h[j].w = __fadd_rn(h[j].w, __fmul_rn(kk, dv.w));
+      acc.x = fmaf(h[j].x, qq, acc.x); acc.y = fmaf(h[j].y, qq, acc.y);
+      acc.z = fmaf(h[j].z, qq, acc.z); acc.w = fmaf(h[j].w, qq, acc.w);
+      *reinterpret_cast<float4*>(hout + row * kF + c0) = h[j];
+    }
+    __syncthreads();                                   // every warp has read the first sums
+    *reinterpret_cast<float4*>(&red[warp][c0]) = acc;
+    __syncthreads();
+    if (tid < kF) {
+      float o = red[0][tid];
+#pragma unroll
+      for (int w = 1; w < kThreads / 32; ++w) o += red[w][tid];
+      store_from_float(a.o, nh * kF + tid, a.o_dtype, o);
+    }
+    __syncthreads();                                   // red, sk, sq are rewritten by the next tile
+  }
+}
+
 constexpr size_t kMaxSmem = 227 * 1024;
 
 }  // namespace
@@ -265,6 +332,15 @@ int launch_generic(const KParams& p, cudaStream_t stream) {
 }
 
 int launch_fp32(const CarryGdnFp32Args& a, cudaStream_t stream) {
+  const long long all_tiles = (long long)a.B * a.HV;
+  if (all_tiles == 0) return CARRY_GDN_OK;
+  if (a.K == kF && a.V == kF && ((uintptr_t)a.h_in % 16) == 0 && ((uintptr_t)a.h_out % 16) == 0) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long cap = (long long)sms * 2 * 8;      // 2 CTAs per SM, a few tiles each
+    gdn_fp32_tile128_kernel<<<(unsigned)(all_tiles < cap ? all_tiles : cap), kThreads, 0, stream>>>(a);
+    return cudaGetLastError() == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
+  }
   const size_t smem = sizeof(float) * ((size_t)a.K * a.V + 2 * (size_t)a.K);
   if (smem > kMaxSmem) return CARRY_GDN_ERR_UNSUPPORTED;
   static thread_local size_t configured[64] = {0};

@@ -4,7 +4,7 @@
 
 ``gdn_quant_step_fused`` (``[B, HV, K, V]`` layout, HV = 32, K = V = 128, fp32
 q/k/v, 8-bit state) for every residual format and both residual-scale
-granularities, CUDA events around 50 calls after 3 warm-up calls.  The figure
+granularities, and ``gdn_step_fused_fp32`` (the unquantised step), CUDA events around 50 calls after 3 warm-up calls.  The figure
 includes the op's own work per call (five output allocations, the ctypes
 call), which is what dominates at 8 requests.  Prints one JSON object.
 """
@@ -52,6 +52,26 @@ def run(batches=(8, 64, 256), calls=50):
             us = e0.elapsed_time(e1) * 1e3 / calls
             state_bytes = B * HV * K * V * 2 * (1 + RESID_BYTES[res_fmt])      # codes + residual, read and written
             row[name] = {"us_per_step": us, "state_GBps": state_bytes / us / 1e3}
+        # the unquantised arm: fp32 state read and written once
+        g = torch.Generator().manual_seed(0)
+        h = (torch.randn(B, HV, K, V, generator=g) * 0.12).to(dev)
+        q = torch.randn(B, HV, K, generator=g).to(dev)
+        k = (torch.randn(B, HV, K, generator=g) * K ** -0.5).to(dev)
+        v = torch.randn(B, HV, V, generator=g).to(dev)
+        alpha = torch.full((B, HV), 0.98, device=dev)
+        beta = torch.rand(B, HV, generator=g).to(dev)
+        call = lambda: sq.gdn_step_fused_fp32(h, q, k, v, alpha, beta)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(calls):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / calls
+        row["fp32_state_unquantised"] = {"us_per_step": us, "state_GBps": B * HV * K * V * 8 / us / 1e3}
         res[f"B{B}"] = row
     return res
 
