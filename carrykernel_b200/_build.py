@@ -19,7 +19,7 @@ CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libcarry_gdn.so")
 SOURCES = ("carry_gdn_api.cu", "carry_gdn_generic.cu", "carry_gdn_tile128.cu",
            "carry_gdn_tile128_vk.cu", "carry_gdn_tile128_kv.cu", "carry_gdn_multi.cu",
-           "carry_gdn_pool.cu")
+           "carry_gdn_pool.cu", "carry_gdn_noef128.cu")
 HEADERS = ("carry_gdn_common.cuh", "carry_gdn_tile128.cuh", "carry_gdn_slot_tile.inc", os.path.join("..", "..", "include", "carry_gdn.h"))
 NVCC_FLAGS = ("-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xptxas", "-v", "-Xcompiler", "-fPIC")

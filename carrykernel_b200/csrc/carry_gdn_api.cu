@@ -17,6 +17,11 @@ int dispatch(const carry::KParams& p, cudaStream_t stream) {
     if (rc == CARRY_GDN_OK) g_last_kernel = 2;
     return rc;
   }
+  if (carry::noef128_eligible(p)) {
+    const int rc = carry::launch_noef128(p, stream);
+    if (rc == CARRY_GDN_OK) g_last_kernel = 5;
+    return rc;
+  }
   const int rc = carry::launch_generic(p, stream);
   if (rc == CARRY_GDN_OK) g_last_kernel = 1;
   return rc;

@@ -190,6 +190,8 @@ bool tile128_eligible(const KParams& p);
 int launch_tile128(const KParams& p, cudaStream_t stream);
 int launch_multi(const KParams& p, int T, long long stride_mixed_t, long long stride_a_t, long long stride_b_t,
                  cudaStream_t stream);
+bool noef128_eligible(const KParams& p);
+int launch_noef128(const KParams& p, cudaStream_t stream);
 int launch_pool_store(const CarryGdnPoolStoreArgs& a, cudaStream_t stream);
 int launch_pool_load(const CarryGdnPoolLoadArgs& a, cudaStream_t stream);
 int launch_pool_copy(const CarryGdnPoolCopyArgs& a, cudaStream_t stream);

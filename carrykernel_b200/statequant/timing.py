@@ -52,6 +52,28 @@ def run(batches=(8, 64, 256), calls=50):
             us = e0.elapsed_time(e1) * 1e3 / calls
             state_bytes = B * HV * K * V * 2 * (1 + RESID_BYTES[res_fmt])      # codes + residual, read and written
             row[name] = {"us_per_step": us, "state_GBps": state_bytes / us / 1e3}
+        # no error feedback: codes read and written once, one state scale per V column or per head
+        for mode in ("v", "head"):
+            g = torch.Generator().manual_seed(0)
+            h0 = (torch.randn(B, HV, K, V, generator=g) * 0.12).to(dev)
+            st = sq.init_quant_state(h0, 8, sq.RES_NONE, state_scale=mode)
+            q = torch.randn(B, HV, K, generator=g).to(dev)
+            k = (torch.randn(B, HV, K, generator=g) * K ** -0.5).to(dev)
+            v = torch.randn(B, HV, V, generator=g).to(dev)
+            alpha = torch.full((B, HV), 0.98, device=dev)
+            beta = torch.rand(B, HV, generator=g).to(dev)
+            call = lambda: sq.gdn_quant_step_fused(*st, q, k, v, alpha, beta, 8, sq.RES_NONE, state_scale=mode)
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(calls):
+                call()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / calls
+            row[f"no_feedback_scale_per_{mode}"] = {"us_per_step": us, "state_GBps": B * HV * K * V * 2 / us / 1e3}
         # the unquantised arm: fp32 state read and written once
         g = torch.Generator().manual_seed(0)
         h = (torch.randn(B, HV, K, V, generator=g) * 0.12).to(dev)

@@ -291,7 +291,8 @@ int carry_gdn_abi_version(void);
 /*
  * Which kernel the last successful call on this host thread selected:
  * 0 = none yet, 1 = generic tile kernel, 2 = 128x128 streaming kernel,
- * 3 = multi-token kernel, 4 = a pool store / load / copy kernel.
+ * 3 = multi-token kernel, 4 = a pool store / load / copy kernel,
+ * 5 = 128x128 kernel of the step without error feedback.
  * Diagnostic only (tests use it to prove which path ran).
  */
 int carry_gdn_last_kernel(void);

@@ -118,6 +118,16 @@ def test_bit_widths_and_uniform_grid(bits):
     got = sq.gdn_quant_step_fused(*_to_dev(st), *_to_dev([q, k, v, alpha, beta]), bits=bits,
                                   res_fmt=sq.RES_NONE, state_scale="head")
     check_quant_step(got, ref, orc.RES_NONE, what=f"bits{bits} uniform")
+    from carrykernel_b200 import _lib
+    assert _lib.load_library().carry_gdn_last_kernel() == 5, "the 128x128 no-feedback kernel should have served this"
+
+    # no feedback with one scale per V column, bf16 activations, in the same kernel
+    qb, kb, vb = q.bfloat16(), k.bfloat16(), v.bfloat16()
+    st = orc.init_quant_state(h0, bits, orc.RES_NONE)
+    ref = orc.quant_step(*st, qb, kb, vb, alpha, beta, bits, orc.RES_NONE)
+    got = sq.gdn_quant_step_fused(*_to_dev(st), *_to_dev([qb, kb, vb, alpha, beta]), bits=bits, res_fmt=sq.RES_NONE)
+    check_quant_step(got, ref, orc.RES_NONE, what=f"bits{bits} per-V, no feedback")
+    assert _lib.load_library().carry_gdn_last_kernel() == 5
 
 
 def test_fp32_step():
