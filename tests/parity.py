@@ -56,6 +56,23 @@ def seeded_inputs(B, HV, K, V, seed=0, T=None, dtype=torch.float32, alpha_mode="
     return h0, q.to(dtype), k.to(dtype), v.to(dtype), alpha, beta
 
 
+def make_packed_inputs(B, H, HV, K, V, seed, dtype=torch.float32, qk_gain=1.0):
+    """Packed activations and gates (recipe of the reference's slot-path tests).
+    ``qk_gain`` scales q and k: with the in-kernel L2 norm off, raw N(0,1) keys of
+    norm ~sqrt(K) make ``v - h^T k`` cancel badly and the step ill-conditioned, so
+    the oracle comparisons without the norm use ``K**-0.5``."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, H, K, generator=g) * qk_gain
+    k = torch.randn(B, H, K, generator=g) * qk_gain
+    v = torch.randn(B, HV, V, generator=g)
+    mixed = torch.cat([q.reshape(B, -1), k.reshape(B, -1), v.reshape(B, -1)], dim=1).contiguous()
+    a = torch.randn(B, HV, generator=g) * 0.5
+    b = torch.randn(B, HV, generator=g)
+    A_log = torch.randn(HV, generator=g) * 0.2
+    dt_bias = torch.randn(HV, generator=g) * 0.1
+    return mixed.to(dtype), a.to(dtype), b.to(dtype), A_log, dt_bias
+
+
 def code_flips(got: torch.Tensor, ref: torch.Tensor):
     """Returns ``(mask_of_differing, fraction, max_abs_diff)`` for integer codes."""
     d = (got.to(torch.int32) - ref.to(torch.int32)).abs()

@@ -223,3 +223,58 @@ def test_oracle_equals_live_reference():
                 else:
                     assert torch.equal(x, y)
             st_r, st_o = r[1:], o[1:]
+
+
+SLOT_STEP_CASES = {   # name -> (H, HV, K, V, resid_fmt, l2norm), as recorded by tests/golden/make_slot_golden.py
+    "k64_int8_l2": (2, 4, 64, 64, 0, True), "k64_int4_l2": (2, 4, 64, 64, 1, True),
+    "k64_int8_raw": (2, 4, 64, 64, 0, False), "k128_int8_l2": (1, 2, 128, 128, 0, True),
+    "k128_int4_l2": (1, 2, 128, 128, 1, True), "k128_int4_raw": (1, 2, 128, 128, 1, False),
+}
+
+
+@pytest.mark.parametrize("name", sorted(SLOT_STEP_CASES))
+def test_slot_step_matches_reference_kernel_recording(name):
+    """``packed_decode_step`` against what the reference's own Triton kernel
+    (vllm_integration/quantized_packed_decode.py:101-327) produced on a B200 from the
+    same pool and activations: codes up to the parity rule (a different summation order
+    moves a few rounding ties), scales and outputs within tolerance, the padding
+    request's row zero, every slot outside the batch untouched."""
+    import parity
+    H, HV, K, V, fmt, l2 = SLOT_STEP_CASES[name]
+    g = load_golden("slot_step_" + name)
+    pool = [g["in_sc"].clone(), g["in_ss"].clone(), g["in_rc"].clone(), g["in_rs"].clone()]
+    assert int(g["in_rc"].abs().sum()) > 0                     # the recorded step starts from a non-zero residual
+    out = torch.full(tuple(g["out"].shape), float("nan"))
+    orc.packed_decode_step(g["mixed"], g["a"], g["b"], g["A_log"], g["dt_bias"], K ** -0.5, *pool, out,
+                           g["slots"], use_qk_l2norm_in_kernel=l2, resid_fmt=fmt)
+    live = [s for s in g["slots"].tolist() if s > 0]
+    parity.assert_close(out, g["out"], f"{name}: out")
+    ref = [g["out_sc"], g["out_ss"], g["out_rc"], g["out_rs"]]
+    # int8 residual codes: one unit in the last place of a target moves r / es by about 1e-3 of a
+    # code, so the reference's own two implementations (this Triton recording and its torch CPU
+    # code, which the oracle equals bit for bit) sit 7-9e-4 apart on large samples; these fixtures
+    # hold 32-65 k elements, hence the wider allowance for that format only.
+    parity.check_pool(pool, ref, fmt == orc.RESID_INT4, live, orc.unpack_int4, name,
+                      max_frac=parity.MAX_FLIP_FRAC if fmt == orc.RESID_INT4 else 2e-3)
+    pad = [n for n, s in enumerate(g["slots"].tolist()) if s <= 0]
+    assert pad and torch.all(out[pad] == 0) and torch.all(g["out"][pad] == 0)
+    untouched = [s for s in range(pool[0].shape[0]) if s not in live]
+    for x, y, z in zip(pool, ref, (g["in_sc"], g["in_ss"], g["in_rc"], g["in_rs"])):
+        assert torch.equal(x[untouched], z[untouched]) and torch.equal(y[untouched], z[untouched])
+
+
+def test_slot_step_ties_match_reference_kernel_recording():
+    """The reference's constructed rounding-tie step (test_quantized_packed_decode.py:211-286) as its
+    Triton kernel executed it: the oracle must reproduce every tensor exactly."""
+    g = load_golden("slot_step_ties")
+    H, HV, K, V = 1, 1, 32, 4
+    pool = [g["in_sc"].clone(), g["in_ss"].clone(), g["in_rc"].clone(), g["in_rs"].clone()]
+    out = torch.empty(1, 1, HV, V)
+    orc.packed_decode_step(torch.zeros(1, 2 * H * K + HV * V), torch.full((1, HV), -60.0), torch.full((1, HV), -60.0),
+                           torch.zeros(HV), torch.zeros(HV), K ** -0.5, *pool, out,
+                           torch.tensor([1], dtype=torch.int32))
+    for x, key in zip(pool, ("out_sc", "out_ss", "out_rc", "out_rs")):
+        assert torch.equal(x, g[key]), key
+    target = g["in_sc"][1].float() * 127.0 + g["in_rc"][1].float() * 0.5
+    assert int(((target.abs() % 1.0) == 0.5).sum()) > 0
+    assert torch.equal(g["out_sc"][1].float(), torch.round(target).clamp(-127, 127))
