@@ -73,10 +73,6 @@ int packed_params(const CarryGdnPackedArgs* a, KParams& p) {
   p.slot_idx = a->ssm_state_indices; p.stride_idx = a->stride_indices;
   p.num_slots = a->num_slots;
   p.out = a->out;
-#ifdef CARRY_PROFILE
-  p.prof = reinterpret_cast<long long*>(a->status);   // debug builds reuse the status pointer (8 x int64)
-  p.status = nullptr;
-#endif
   return CARRY_GDN_OK;
 }
 }  // namespace carry

@@ -58,9 +58,6 @@ struct KParams {
   long long stride_idx;
   int num_slots;
   void* out;
-#ifdef CARRY_PROFILE
-  long long* prof;   // debug builds only: per-phase cycle counters
-#endif
 };
 
 __device__ __forceinline__ float load_as_float(const void* p, long long i, int dtype) {

@@ -117,8 +117,6 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
     const float2 magic2 = splat(kMagicRound), nmagic2 = splat(-kMagicRound);
     const long long out_tok = out_tok0 + (long long)t * out_tok_stride;
 
-#undef PROF_MARK
-#define PROF_MARK(k)
 #define CARRY_SLOT_VEC_Q (&vec_t[tc][0])
 #define CARRY_SLOT_VEC_K (&vec_t[tc][L::kVecBytes])
 #define CARRY_SLOT_VEC_V (&vec_t[tc][2 * L::kVecBytes])
@@ -141,7 +139,6 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
 #define CARRY_SLOT_PUT_RSCALE_V(r0_, v4_) *reinterpret_cast<uint4*>(sb + L::kRScale + (r0_) * 4) = (v4_)
 #define CARRY_SLOT_PUT_RSCALE_HEAD(bits_) reinterpret_cast<uint32_t*>(sb + L::kRScale)[hv & 3] = (bits_)
 #include "carry_gdn_slot_tile.inc"
-#undef PROF_MARK
 #undef CARRY_SLOT_VEC_Q
 #undef CARRY_SLOT_VEC_K
 #undef CARRY_SLOT_VEC_V

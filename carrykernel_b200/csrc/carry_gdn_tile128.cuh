@@ -182,6 +182,13 @@ template <int A, int B>
 __device__ __forceinline__ float2 s8x2_cvt(uint32_t w) {
   return make_float2((float)(signed char)((w >> (8 * A)) & 0xffu), (float)(signed char)((w >> (8 * B)) & 0xffu));
 }
+// bytes A and B of w, each a nibble in offset binary (0..15 = code + 8) -> {136 + code A, 136 + code B}:
+// the byte is placed right above the low half-word of a float whose exponent byte says 128
+template <int A, int B>
+__device__ __forceinline__ float2 nib2_biased(uint32_t w) {
+  return make_float2(__uint_as_float(__byte_perm(w, 0x43000000u, 0x7044 | (A << 8))),
+                     __uint_as_float(__byte_perm(w, 0x43000000u, 0x7044 | (B << 8))));
+}
 // four fp8-e5m2 values in a word -> floats.  An e5m2 value is the upper byte of the half with the same
 // value, so each pair of bytes becomes a half2 by one byte permute.
 __device__ __forceinline__ void e5m2x4_to_float(uint32_t w, float2& ab, float2& cd) {
@@ -315,12 +322,8 @@ struct StageLayout {
   static_assert(kBytes % 128 == 0, "stages keep the ring's 128-byte alignment");
   // Two groups of 8 warps share one CTA (and one SM) when at least 2 stages per group fit (every
   // variant today; 128 registers per thread then), else the CTA is a single group.
-#ifdef CARRY_FORCE_1GROUP
-  static constexpr int kGroups = 1;
-#else
   static constexpr int kGroups =
       ((4 * kBytes + 2 * kStaticOf(LAYOUT) <= kSmemPerCta) ? 2 : 1);
-#endif
   static constexpr int kStatic = kGroups * kStaticOf(LAYOUT);
   static constexpr int kBudget = kSmemPerCta - kStatic;
   static constexpr int kFit = kBudget / kBytes;
@@ -611,9 +614,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   const int grp = (G == 1) ? 0 : (warp >> 3), gw = warp & 7, gtid = tid & (kThreads - 1);
   const int bar0 = 3 * grp;                          // this group's named barriers are bar0 + 1 .. bar0 + 3
   float* col_red = col_red_all + ((LAYOUT == LAYOUT_KV) ? grp * kWarps * kT * 4 : 0);
-#ifdef CARRY_PROFILE
-  const long long prof_k0 = clock64();
-#endif
   const int total = p.B * p.HV;
   const int my_tiles = (total - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   volatile int* poison = &poison_flag;
@@ -637,9 +637,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   // tiles, four lanes per tile, in one trip to global memory; the rest of the ring is requested after
   // that, so that the first tiles are not queued behind it.  (Gathering first and requesting the whole
   // ring afterwards was measured 3 us slower per launch.)
-#ifdef CARRY_PROFILE
-  const long long prof_p1 = clock64();
-#endif
   // (the last warps make these requests: the first warps are the ones with tiles to prepare when a CTA
   // has few, and a request worked out from scratch is a long chain of one thread's instructions)
   if (lane == 0 && warp >= G * kWarps - G && (G * kWarps - 1 - warp) < my_tiles) {
@@ -651,9 +648,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], tn, thv, th, tslot);
   }
   __syncwarp();
-#ifdef CARRY_PROFILE
-  const long long prof_p2 = clock64();
-#endif
   {
     static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
     const int i = tid >> 2;
@@ -662,14 +656,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
                                    &meta_cache[i], &desc_cache[i]);
   }
-#ifdef CARRY_PROFILE
-  const long long prof_p3 = clock64();
-#endif
   __syncthreads();
   static_assert(S <= G * kWarps && S <= kTileCache, "one warp per stage issues the first requests, from the cache");
-#ifdef CARRY_PROFILE
-  const long long prof_p4 = clock64();
-#endif
 
   const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
   const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
@@ -703,13 +691,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     if (gw == (cnt & (kWarps - 1)) && lane == 0 && num + S < my_tiles && !*poison) load_tile(num + S);
   };
 
-#ifdef CARRY_PROFILE
-  long long prof_acc[12] = {0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0, 0};
-  long long prof_t = clock64();
-#define PROF_MARK(k) { const long long now_ = clock64(); prof_acc[k] += now_ - prof_t; prof_t = now_; }
-#else
-#define PROF_MARK(k)
-#endif
   int it = grp;                                      // number of the tile in hand
   for (int cnt = 0; it < my_tiles; ++cnt) {
     const int s = it % S;
@@ -726,7 +707,6 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const int n = (int)tm0.x, hv = (int)(tm0.y & 0xffffu);
 
     const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
-    PROF_MARK(0)
     const int slot = (int)tm0.z;
     const int out_row = n * p.HV + hv;                // outputs of this tile start at element out_row * 128
     const bool live = slot > 0 && healthy;
@@ -771,8 +751,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 #define CARRY_SLOT_MEET(statement)                \
   if (lane == 0) { statement; claim_next(cnt); }  \
   warps_meet(bar0 + 3);                           \
-  refill_stage(cnt, it);                          \
-  PROF_MARK(5)
+  refill_stage(cnt, it)
 #define CARRY_SLOT_RESID_BEGIN() const unsigned long long dst_resid = dst_of(D_RESID)
 #define CARRY_SLOT_PUT_RESID4(i_, r0_, c0_, w_)                                    \
   {                                                                                \
@@ -1018,24 +997,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
         }
       }
     }
-    PROF_MARK(6)
-
     it = *reinterpret_cast<volatile int*>(&claimed[grp][cnt & 1]);   // written before this tile's last meeting
   }
-#ifdef CARRY_PROFILE
-  if (lane == 0 && p.prof) {
-    unsigned long long* pp = reinterpret_cast<unsigned long long*>(p.prof);
-    const unsigned long long cyc = (unsigned long long)(clock64() - prof_k0);
-    for (int k = 0; k < 12; ++k) atomicAdd(pp + k, (unsigned long long)prof_acc[k]);
-    atomicMax(pp + 80, cyc);                     // the warp that ran longest, cycles
-    atomicAdd(pp + 84, cyc);                     // all warps' cycles from kernel start to here
-    atomicMin(pp + 82, cyc);                     // the warp that was done first
-    atomicAdd(pp + 85, (unsigned long long)(prof_p1 - prof_k0));
-    atomicAdd(pp + 86, (unsigned long long)(prof_p2 - prof_p1));
-    atomicAdd(pp + 87, (unsigned long long)(prof_p3 - prof_p2));
-    atomicAdd(pp + 88, (unsigned long long)(prof_p4 - prof_p3));
-  }
-#endif
   __syncthreads();
 }
 
@@ -1071,12 +1034,8 @@ int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-#ifdef CARRY_NO_PDL
-  cfg.numAttrs = 0;
-#else
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-#endif
   const cudaError_t err = cudaLaunchKernelEx(&cfg, kern, p);
   if (err != cudaSuccess) cudaGetLastError();
   return err == cudaSuccess ? CARRY_GDN_OK : CARRY_GDN_ERR_LAUNCH;
