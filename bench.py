@@ -17,9 +17,14 @@ ranks of the elapsed time.
     python bench.py --gpus 1 --steps 20 --warmup 5
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
-    python bench.py --impl reference --steps 20 --warmup 5     # CPU arm (oracle port)
+    python bench.py --impl reference --steps 20 --warmup 5     # CPU arm: the reference's own CPU step
+    python bench.py --strong 512 --layers 4                    # one global batch split over the ranks
+    python bench.py --config 5                                 # bit-width / granularity sweep (512 chained steps)
 
-One JSON line goes to stdout (rank 0).
+One JSON line goes to stdout (rank 0).  At one GPU the line also carries the
+metric's other batch sizes (``sweep``: 128 / 256 / 512 requests per launch) and
+the bit-width sweep (``config5``); at N GPUs it carries every rank's time and a
+strong-scaling point (512 requests split over the ranks).
 """
 
 from __future__ import annotations
@@ -57,11 +62,22 @@ TILE_BYTES = 2 * K * V + 2 * (K * V // 2) + 2 * V * 4 + 2 * 4 + 2 * K * 2 + V * 
 SLOT_LAYER_BYTES = HV * TILE_BYTES + 4          # + the int32 slot id
 assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant
-# kernel on this workload (64 requests), from the ncu capture summarised under
-# profiles/gdn_tile128_int4_perhead_bf16_b64.md (mean of six steady-state launches, ncu with
-# --cache-control none so that the write-back of the results is inside the window).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 103_320_000
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel on this workload
+# (64 requests; mean of six steady-state launches, ncu with --cache-control none so that the write-back
+# of the results is inside the window), keyed by the SHA-256 of the kernel sources the profiled library
+# was built from.  A library built from other sources gets null until it has been profiled again.
+NCU_TRAFFIC_BY_SOURCE = {
+}
+KERNEL_SOURCES = ("carry_gdn_tile128.cuh", "carry_gdn_slot_tile.inc", "carry_gdn_common.cuh")
+
+
+def kernel_source_hash():
+    import hashlib
+    h = hashlib.sha256()
+    for name in KERNEL_SOURCES:
+        with open(os.path.join(ROOT, "carrykernel_b200", "csrc", name), "rb") as f:
+            h.update(f.read())
+    return h.hexdigest()[:16]
 
 
 def parse_args():
@@ -84,6 +100,16 @@ def parse_args():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--e2e-groups", type=int, default=E2E_GROUPS,
                     help="layer groups of the host-buffer pipeline (copy in / compute / copy out overlap per group)")
+    ap.add_argument("--repeats", type=int, default=5,
+                    help="the timed region (--steps replays) is measured this many times; the median is reported")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the batch sweep, the strong-scaling point and the bit-width sweep (profiler runs)")
+    ap.add_argument("--strong", type=int, default=0, metavar="B",
+                    help="strong scaling: one global batch of B requests, its slots split evenly over the ranks")
+    ap.add_argument("--config", type=int, choices=[3, 5], default=3,
+                    help="3: the serving step (default); 5: bit-width / granularity sweep over 512 chained steps")
+    ap.add_argument("--c5-batch", type=int, default=256)
+    ap.add_argument("--c5-steps", type=int, default=512)
     return ap.parse_args()
 
 
@@ -104,13 +130,36 @@ def peak_hbm():
 class Workload:
     """Per-GPU state and inputs of the decode step, resident in HBM."""
 
-    def __init__(self, device, batch, layers, resid, seed, resid_scale="head"):
+    def __init__(self, device, batch, layers, resid, seed, resid_scale="head", shard=None):
+        """``shard=(world, rank)``: ``batch`` is a global batch whose slot ids and activations every
+        rank draws identically from ``seed``; this rank keeps the requests whose slots it owns
+        (``sharding.shard_requests``) in a pool of its share of the slots."""
         from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
-        self.qpd, self.device, self.batch, self.layers = qpd, device, batch, layers
+        from carrykernel_b200 import sharding
+        self.qpd, self.device, self.layers = qpd, device, layers
         self.resid_fmt = qpd.RESID_INT4 if resid == "int4" else qpd.RESID_INT8
         g = torch.Generator().manual_seed(seed)
         width = 2 * H * K + HV * V
-        slots = max(POOL_SLOTS, batch) + 1
+        global_batch, global_slots = batch, max(POOL_SLOTS, batch) + 1
+        self.rows = []                                   # strong scaling: this rank's rows of the global batch, per layer
+        if shard is not None:
+            world, rank = shard
+            drawn = []
+            for l in range(layers):                      # same draws on every rank
+                idx = (torch.randperm(global_slots - 1, generator=g)[:global_batch] + 1).to(torch.int32)
+                mixed = torch.randn(global_batch, width, generator=g).to(torch.bfloat16)
+                a = torch.randn(global_batch, HV, generator=g).to(torch.bfloat16)
+                b = torch.randn(global_batch, HV, generator=g).to(torch.bfloat16)
+                rows, local = sharding.shard_requests(idx, global_slots, world, rank)
+                drawn.append((local, mixed[rows], a[rows], b[rows]))
+                self.rows.append(rows)
+            # every layer's shard padded to the largest one with padding requests (slot 0), so that one
+            # buffer layout serves all layers
+            batch = max(1, max(len(d[0]) for d in drawn))
+            slots = sharding.local_pool_slots(global_slots, world, rank)
+        else:
+            slots = global_slots
+        self.batch = batch
         self.num_slots = slots
         self.pools, self.indices, self.mixed, self.a, self.b, self.out = [], [], [], [], [], []
         # activations of all layers in one device buffer, outputs in another (per-layer views into
@@ -139,10 +188,17 @@ class Workload:
             for name, shape, dt in seg:
                 views[name] = view(self.in_dev, off, shape, dt)
                 off += up(math.prod(shape) * torch.empty((), dtype=dt).element_size())
-            views["idx"].copy_((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32))
-            views["mixed"].copy_(torch.randn(batch, width, generator=g).to(torch.bfloat16))
-            views["a"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
-            views["b"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
+            if shard is not None:
+                local, mixed_l, a_l, b_l = drawn[l]
+                n = len(local)
+                views["idx"].zero_(); views["mixed"].zero_(); views["a"].zero_(); views["b"].zero_()
+                views["idx"][:n].copy_(local); views["mixed"][:n].copy_(mixed_l)
+                views["a"][:n].copy_(a_l); views["b"][:n].copy_(b_l)
+            else:
+                views["idx"].copy_((torch.randperm(slots - 1, generator=g)[:batch] + 1).to(torch.int32))
+                views["mixed"].copy_(torch.randn(batch, width, generator=g).to(torch.bfloat16))
+                views["a"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
+                views["b"].copy_(torch.randn(batch, HV, generator=g).to(torch.bfloat16))
             self.indices.append(views["idx"]); self.mixed.append(views["mixed"])
             self.a.append(views["a"]); self.b.append(views["b"])
             self.out.append(view(self.out_dev, l * self.out_layer_bytes, (batch, 1, HV, V), torch.bfloat16))
@@ -244,7 +300,7 @@ def time_graph(graph, steps, device):
     return start.elapsed_time(end) * 1e-3
 
 
-def e2e_run(wl, steps, warmup, groups):
+def e2e_run(wl, steps, warmup, groups, kernels=True):
     """The same step through the public call with HOST buffers.  Every step copies all activations and
     slot ids from pinned host memory to the device, runs the 24 layer calls, and copies every output
     row back to pinned host memory; the step ends when the host holds all outputs (stream
@@ -252,7 +308,8 @@ def e2e_run(wl, steps, warmup, groups):
     are already on their way in and the previous group's outputs on their way out, each on its own
     stream.  The whole step -- copies, layer calls through the public function, the events that order
     them -- is captured once as one CUDA graph and replayed per step, as a serving engine would.  The
-    state pools stay in HBM between steps: they are the recurrent state."""
+    state pools stay in HBM between steps: they are the recurrent state.  ``kernels=False`` replays the
+    very same graph shape without the layer calls: the floor that the host copies alone set."""
     dev = wl.device
     L = wl.layers
     groups = max(1, min(groups, L))
@@ -269,9 +326,10 @@ def e2e_run(wl, steps, warmup, groups):
             with torch.cuda.stream(s_in):
                 wl.in_dev[a:b].copy_(in_host[a:b], non_blocking=True)
             s_run.wait_stream(s_in)
-            with torch.cuda.stream(s_run):
-                for l in range(lo, hi):
-                    wl.layer_step(l)
+            if kernels:
+                with torch.cuda.stream(s_run):
+                    for l in range(lo, hi):
+                        wl.layer_step(l)
             s_out.wait_stream(s_run)
             a, b = lo * wl.out_layer_bytes, hi * wl.out_layer_bytes
             with torch.cuda.stream(s_out):
@@ -389,29 +447,63 @@ def cpu_baseline_and_parity(wl, resid, resid_scale="head"):
 
 
 def run_reference_arm(args, rank):
-    """--impl reference: the reference's CPU algorithm (oracle port) on the host
-    cores.  One step is a bounded sample: 1 layer x 16 requests."""
+    """--impl reference: the reference's CPU implementation of the step on the host cores.
+
+    With the staged copy of the reference present (``oracle/make_ref.py``), its own
+    ``gdn_quant_step_torch`` (statequant/kernel.py:149-178) is what runs: the fused step in its
+    ``[B, HV, K, V]`` layout with the int8 residual and per-column scales, the only CPU code the
+    reference has for this step (the slot-indexed int4 / per-head variant exists there as a Triton
+    kernel only).  Same state size per slot-layer-step, same input laws.  Without the copy the
+    oracle port of the slot-indexed step is timed instead.  One step is a bounded sample: 1 layer
+    x 16 requests."""
     if rank != 0:
         return
+    from oracle import make_ref
     s_batch, s_layers = 16, 1
     torch.set_num_threads(os.cpu_count() or 1)
-    sample, fmt = cpu_sample_inputs(s_batch, s_layers, args.resid)
+    ref = make_ref.ref_path()
+    if ref is not None:
+        sys.path.insert(0, ref)
+        from statequant import kernel as rk
+        g = torch.Generator().manual_seed(1234)
+        h0 = torch.randn(s_batch, HV, K, V, generator=g) * 0.124
+        st = rk.init_quant_state(h0, 8, rk.RES_INT8)
+        q = torch.nn.functional.normalize(torch.randn(s_batch, HV, K, generator=g), dim=-1)
+        k = torch.nn.functional.normalize(torch.randn(s_batch, HV, K, generator=g), dim=-1)
+        v = torch.randn(s_batch, HV, V, generator=g)
+        alpha = torch.exp(-0.1 * torch.nn.functional.softplus(torch.randn(s_batch, HV, generator=g)))
+        beta = torch.sigmoid(torch.randn(s_batch, HV, generator=g))
+
+        def one_pass():
+            nonlocal st
+            st = rk.gdn_quant_step_torch(*st, q, k, v, alpha, beta, 8, rk.RES_INT8)[1:]
+        kind = "reference"
+        desc = (f"{s_layers} layer x {s_batch} requests per step through the reference's own CPU step "
+                "gdn_quant_step_torch (statequant/kernel.py:149-178; [B,HV,K,V] layout, int8 residual, per-column "
+                "scales: the reference has no CPU code for the slot-indexed int4 / per-head step), same state "
+                "size and input laws")
+    else:
+        sample, fmt = cpu_sample_inputs(s_batch, s_layers, args.resid)
+
+        def one_pass():
+            cpu_oracle_pass(sample, fmt)
+        kind = "port"
+        desc = f"{s_layers} layer x {s_batch} requests per step (oracle port; same shapes and input laws)"
     for _ in range(max(args.warmup, 1)):
-        cpu_oracle_pass(sample, fmt)
+        one_pass()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        cpu_oracle_pass(sample, fmt)
+        one_pass()
     sec = time.perf_counter() - t0
     units = s_batch * s_layers * args.steps
     value = units / sec
-    desc = f"{s_layers} layer x {s_batch} requests per step (same shapes and input laws)"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": workload_config(args, args.batch, args.layers),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
-                         "kind": "port", "sample": desc},
+                         "kind": kind, "sample": desc},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -446,8 +538,179 @@ def workload_config(args, batch, layers, note=None):
 
 
 # ---------------------------------------------------------------------------
+# the bit-width / granularity sweep (BASELINE config 5)
+# ---------------------------------------------------------------------------
+
+def config5_sweep(batch=256, steps=512, bits=(3, 4, 5, 6, 8), seed=0):
+    """State bits in {3,4,5,6,8}; one scale per head without error feedback (``uniform_quantize``,
+    statequant/quant.py:23-34) against one scale per V column with an fp32 error-feedback residual
+    (``per_axis_quantize(.., -2)`` + ``ErrorFeedback``, statequant/quant.py:37-42,65-80); per-head
+    constant decay from U[0.9, 0.999]; ``steps`` chained decode steps through the library's statequant
+    calls; relative L2 error of the final dequantised state against the fp32 recurrence
+    (``gdn_step_fused_fp32``).  The experiment of experiments/exp2_bits_sweep.py and exp2b_granularity.py
+    at serving size; inputs are generated on the device step by step from fixed seeds."""
+    from carrykernel_b200.statequant import kernel as sq
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(seed)
+    h0 = torch.randn(batch, HV, K, V, generator=g, device=dev) * 0.1
+    alpha = 0.9 + 0.099 * torch.rand(batch, HV, generator=g, device=dev)
+
+    def step_inputs(t):
+        gt = torch.Generator(device=dev).manual_seed(seed * 100003 + t)
+        q = torch.randn(batch, HV, K, generator=gt, device=dev)
+        k = torch.nn.functional.normalize(torch.randn(batch, HV, K, generator=gt, device=dev), dim=-1)
+        v = torch.randn(batch, HV, V, generator=gt, device=dev)
+        beta = torch.sigmoid(torch.randn(batch, HV, generator=gt, device=dev))
+        return q, k, v, beta
+
+    def timed(fn):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return out, e0.elapsed_time(e1) * 1e3 / steps
+
+    def fp32_chain():
+        h = h0.clone()
+        for t in range(steps):
+            q, k, v, beta = step_inputs(t)
+            h, _ = sq.gdn_step_fused_fp32(h, q, k, v, alpha, beta)
+        return h
+
+    def quant_chain(nbits, res_fmt, state_scale):
+        st = sq.init_quant_state(h0, nbits, res_fmt, state_scale=state_scale)
+        for t in range(steps):
+            q, k, v, beta = step_inputs(t)
+            st = sq.gdn_quant_step_fused(*st, q, k, v, alpha, beta, bits=nbits, res_fmt=res_fmt,
+                                         state_scale=state_scale)[1:]
+        codes, scale = st[0], st[1]
+        return codes.float() * (scale[..., None, :] if state_scale == "v" else scale[..., None, None])
+
+    h_ref, us_ref = timed(fp32_chain)
+    norm = h_ref.norm()
+    res = {"batch": batch, "steps": steps, "fp32_us_per_step": us_ref, "rel_l2_error": {}}
+    for nbits in bits:
+        uni, us_u = timed(lambda: quant_chain(nbits, sq.RES_NONE, "head"))
+        err_u = ((uni - h_ref).norm() / norm).item()
+        del uni
+        ef, us_e = timed(lambda: quant_chain(nbits, sq.RES_FP32, "v"))
+        err_e = ((ef - h_ref).norm() / norm).item()
+        del ef
+        res["rel_l2_error"][str(nbits)] = {"per_head_no_ef": err_u, "per_v_ef": err_e,
+                                           "per_head_no_ef_us_per_step": us_u, "per_v_ef_us_per_step": us_e}
+    torch.cuda.empty_cache()
+    return res
+
+
+def run_config5(args):
+    res = config5_sweep(args.c5_batch, args.c5_steps)
+    launches = (1 + 2 * len(res["rel_l2_error"])) * args.c5_steps
+    print(json.dumps({
+        "metric": "final_state_rel_l2_error_8bit_per_v_ef", "value": res["rel_l2_error"]["8"]["per_v_ef"],
+        "unit": "relative L2 error vs the fp32 recurrence", "n_gpus": 1, "steps": args.c5_steps, "warmup": 0,
+        "ms_per_step": res["rel_l2_error"]["8"]["per_v_ef_us_per_step"] * 1e-3, "higher_is_better": False,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "bit-width / granularity sweep: state bits 3,4,5,6,8, per-head scale without error "
+                               "feedback vs per-V scale with fp32 error feedback, per-head decay U[0.9,0.999]",
+                   "requests": args.c5_batch, "chained_steps": args.c5_steps, "HV": HV, "K": K, "V": V},
+        "config5": res, "gpu_launches": launches}))
+
+
+# ---------------------------------------------------------------------------
 # main
 # ---------------------------------------------------------------------------
+
+def capture_step(wl, device):
+    """One decode step (all layers) of ``wl`` as a CUDA graph, warmed."""
+    side = torch.cuda.Stream(device)
+    with torch.cuda.stream(side):
+        wl.step()
+    torch.cuda.synchronize(device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        wl.step()
+    return graph
+
+
+def timed_repeats(graph, steps, repeats, device, world):
+    """``repeats`` measurements of ``steps`` replays each; every one is bracketed by a barrier and a
+    device synchronise on both sides and reduced to the slowest rank.  Returns (per-repeat job times,
+    this rank's own per-repeat times)."""
+    import torch.distributed as dist
+    from carrykernel_b200.sharding import max_over_ranks
+    job, mine = [], []
+    for _ in range(repeats):
+        if world > 1:
+            dist.barrier()
+        t = time_graph(graph, steps, device)
+        if world > 1:
+            dist.barrier()
+        mine.append(t)
+        job.append(max_over_ranks(t, device))
+    return job, mine
+
+
+def median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
+
+
+def roofline_of(args, batch, per_launch, traffic=None, kernel="gdn_tile128_kernel"):
+    peak, peak_kind = peak_hbm()
+    per_slot = SLOT_LAYER_BYTES if args.resid == "int4" else SLOT_LAYER_BYTES + HV * K * V
+    if args.resid_scale == "v":
+        per_slot += HV * (2 * V * 4 - 8)
+    achieved = per_slot * batch / per_launch / 1e9
+    return {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "peak_kind": f"of {peak_kind}", "frac_of_8000": achieved / 8000.0,
+            "bytes_per_launch": per_slot * batch, "traffic": traffic, "kernel": kernel}
+
+
+def batch_sweep(args, device, batches=(128, 256, 512), layers=4, steps=10, repeats=5):
+    """The metric's other batch sizes on this GPU: us per launch, GB/s and fraction of the copy rate
+    at 128 / 256 / 512 requests per launch (4 layers each, every step larger than the L2)."""
+    out = {}
+    for b in batches:
+        wl = Workload(device, b, layers, args.resid, seed=77 + b, resid_scale=args.resid_scale)
+        wl.warm_state(8)
+        graph = capture_step(wl, device)
+        for _ in range(3):
+            graph.replay()
+        job, _ = timed_repeats(graph, steps, repeats, device, 1)
+        per_launch = median(job) / (steps * layers)
+        r = roofline_of(args, b, per_launch)
+        out[str(b)] = {"us_per_launch": per_launch * 1e6, "GBps": r["achieved"], "frac": r["frac"],
+                       "frac_of_8000": r["frac_of_8000"], "layers": layers, "steps": steps,
+                       "spread_us": [min(job) / (steps * layers) * 1e6, max(job) / (steps * layers) * 1e6]}
+        del wl, graph
+        torch.cuda.empty_cache()
+    return out
+
+
+def strong_point(args, device, world, rank, global_batch, layers=4, steps=10, repeats=5):
+    """One global batch of ``global_batch`` requests, its slots split evenly over the ranks
+    (``sharding.shard_requests``); every rank steps the requests it owns; time = slowest rank."""
+    wl = Workload(device, global_batch, layers, args.resid, seed=4242, resid_scale=args.resid_scale,
+                  shard=(world, rank))
+    wl.warm_state(8)
+    graph = capture_step(wl, device)
+    for _ in range(3):
+        graph.replay()
+    job, _ = timed_repeats(graph, steps, repeats, device, world)
+    t = median(job) / steps
+    # reporting only: reassemble layer 0's output rows in global order and reduce them to one number
+    from carrykernel_b200.sharding import gather_rows
+    n0 = len(wl.rows[0])
+    full = gather_rows(wl.rows[0], wl.out[0][:n0].float().cpu(), global_batch)
+    res = {"global_batch": global_batch, "layers": layers, "requests_this_rank": [len(r) for r in wl.rows][:2],
+           "ms_per_step": t * 1e3, "us_per_launch": t / layers * 1e6,
+           "slot_layer_steps_per_s": global_batch * layers / t,
+           "out_checksum": float(full.double().abs().sum())}
+    del wl, graph
+    torch.cuda.empty_cache()
+    return res
+
 
 def main():
     args = parse_args()
@@ -464,6 +727,10 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.config == 5:
+        if rank == 0:
+            run_config5(args)
+        return
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
@@ -472,80 +739,116 @@ def main():
     from carrykernel_b200 import _lib
     lib = _lib.load_library()
 
-    wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank,
-                  resid_scale=args.resid_scale)
+    strong = args.strong > 0
+    if strong:
+        wl = Workload(device, args.strong, args.layers, args.resid, seed=4242, resid_scale=args.resid_scale,
+                      shard=(world, rank))
+    else:
+        wl = Workload(device, args.batch, args.layers, args.resid, seed=1000 + rank,
+                      resid_scale=args.resid_scale)
     wl.warm_state(args.warm_steps)
     kernel_used = lib.carry_gdn_last_kernel()
 
     cpu_base = parity_stats = None
-    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
+    if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline and not strong:
         cpu_base, parity_stats = cpu_baseline_and_parity(wl, args.resid, args.resid_scale)
 
-    # capture one decode step (all layers) in a CUDA graph
-    side = torch.cuda.Stream(device)
-    with torch.cuda.stream(side):
-        wl.step()
-    torch.cuda.synchronize(device)
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=side):
-        wl.step()
+    graph = capture_step(wl, device)
     for _ in range(max(args.warmup, 3)):
         graph.replay()
     torch.cuda.synchronize(device)
 
     sampler = ClockSampler(physical_gpu_index(local_rank))
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize(device)
     sampler.start()
-    elapsed = time_graph(graph, args.steps, device)
+    job, mine = timed_repeats(graph, args.steps, max(args.repeats, 1), device, world)
+    elapsed = median(job)
     # keep the sampler alive long enough for at least a few samples under load
-    if elapsed < args.min_sample_s:
-        reps = int(args.min_sample_s / max(elapsed / args.steps, 1e-6)) + 1
+    if sum(mine) < args.min_sample_s:
+        reps = int((args.min_sample_s - sum(mine)) / max(elapsed / args.steps, 1e-6)) + 1
         time_graph(graph, reps, device)
     clocks = sampler.stop()
-    if world > 1:
-        dist.barrier()
-    from carrykernel_b200.sharding import max_over_ranks
-    elapsed = max_over_ranks(elapsed, device)
 
-    units_per_step = args.batch * args.layers * n_gpus
+    global_batch = args.strong if strong else args.batch * n_gpus
+    units_per_step = global_batch * args.layers
     value = units_per_step * args.steps / elapsed
     per_launch = elapsed / (args.steps * args.layers)
-    peak, peak_kind = peak_hbm()
-    achieved = SLOT_LAYER_BYTES * args.batch / per_launch / 1e9 if args.resid == "int4" else \
-        (SLOT_LAYER_BYTES + HV * K * V) * args.batch / per_launch / 1e9
+
+    per_rank = None
+    if world > 1:
+        # every rank's own median and SM clock, so that a slow rank can be named
+        mine_t = torch.tensor([median(mine), float(clocks["sm_mhz"] or 0)], dtype=torch.float64, device=device)
+        allt = [torch.zeros_like(mine_t) for _ in range(world)]
+        dist.all_gather(allt, mine_t)
+        ms = [float(x[0]) / args.steps * 1e3 for x in allt]
+        slow = max(range(world), key=lambda r: ms[r])
+        per_rank = {"ms_per_step": ms, "min": min(ms), "median": median(ms), "max": max(ms),
+                    "slowest_rank": slow, "slowest_rank_sm_mhz": float(allt[slow][1])}
 
     e2e = None
-    if not args.no_e2e:
+    if not args.no_e2e and not strong:
+        from carrykernel_b200.sharding import max_over_ranks
         t_e2e, h2d, d2h = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups)
         t_e2e = max_over_ranks(t_e2e, device)
+        t_floor, _, _ = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, kernels=False)
+        t_floor = max_over_ranks(t_floor, device)
         e2e = {"value": units_per_step * args.steps / t_e2e, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-               "ms_per_step": t_e2e / args.steps * 1e3}
+               "ms_per_step": t_e2e / args.steps * 1e3,
+               "copy_floor_ms_per_step": t_floor / args.steps * 1e3}
+
+    sweep = strong_pt = c5 = None
+    if not args.no_extras and not strong:
+        if n_gpus == 1:
+            del graph
+            sweep = batch_sweep(args, device)
+        else:
+            strong_pt = strong_point(args, device, world, rank, 512)
+        if rank == 0 and n_gpus == 1 and args.resid == "int4":
+            wl = None
+            torch.cuda.empty_cache()
+            c5 = config5_sweep(args.c5_batch, args.c5_steps)
 
     if rank == 0:
+        traffic = None
+        if args.resid == "int4" and args.batch == BATCH and args.resid_scale == "head" and not strong:
+            traffic = NCU_TRAFFIC_BY_SOURCE.get(kernel_source_hash())
+        cfg = workload_config(args, args.batch if not strong else args.strong, args.layers)
+        if strong:
+            cfg["strong_scaling"] = (f"one global batch of {args.strong} requests; the pool's slots split evenly over "
+                                     f"{n_gpus} ranks, each rank steps the requests whose slots it owns")
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": n_gpus, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": elapsed / args.steps * 1e3,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": workload_config(args, args.batch, args.layers),
+            "higher_is_better": True, "scaling": "strong" if strong else "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": cfg,
             "us_per_token": elapsed / args.steps * 1e6,
             "us_per_layer_step": per_launch * 1e6,
-            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                         "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
-                         "frac_of_8000": achieved / 8000.0,
-                         "bytes_per_launch": SLOT_LAYER_BYTES * args.batch,
-                         "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH if (args.resid == "int4" and args.batch == BATCH
-                                                                     and args.resid_scale == "head") else None,
-                         "kernel": {1: "gdn_generic_kernel", 2: "gdn_tile128_kernel"}.get(kernel_used, "?")},
+            "repeats": {"n": len(job), "ms_per_step_min": min(job) / args.steps * 1e3,
+                        "ms_per_step_median": elapsed / args.steps * 1e3,
+                        "ms_per_step_max": max(job) / args.steps * 1e3},
+            "roofline": roofline_of(args, wl_batch_for_roofline(args, strong, n_gpus), per_launch, traffic,
+                                    {1: "gdn_generic_kernel", 2: "gdn_tile128_kernel"}.get(kernel_used, "?")),
             "cpu_baseline": cpu_base, "parity": parity_stats, "e2e": e2e,
             "gpu_launches": args.steps * args.layers, "clocks": clocks,
+            "kernel_source_hash": kernel_source_hash(),
         }
+        if per_rank is not None:
+            line["per_rank"] = per_rank
+        if sweep is not None:
+            line["sweep"] = sweep
+        if strong_pt is not None:
+            line["strong"] = strong_pt
+        if c5 is not None:
+            line["config5"] = c5
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+def wl_batch_for_roofline(args, strong, n_gpus):
+    """Requests one launch of one rank processes (the roofline is per GPU)."""
+    return (args.strong + n_gpus - 1) // n_gpus if strong else args.batch
 
 
 if __name__ == "__main__":
