@@ -20,6 +20,7 @@ ranks of the elapsed time.
     python bench.py --impl reference --steps 20 --warmup 5     # CPU arm: the reference's own CPU step
     python bench.py --strong 512 --layers 4                    # one global batch split over the ranks
     python bench.py --config 5                                 # bit-width / granularity sweep (512 chained steps)
+    python bench.py --mode headtohead | statequant | multi | pool   # side measurements
 
 One JSON line goes to stdout (rank 0).  At one GPU the line also carries the
 metric's other batch sizes (``sweep``: 128 / 256 / 512 requests per launch) and
@@ -108,6 +109,12 @@ def parse_args():
                     help="strong scaling: one global batch of B requests, its slots split evenly over the ranks")
     ap.add_argument("--config", type=int, choices=[3, 5], default=3,
                     help="3: the serving step (default); 5: bit-width / granularity sweep over 512 chained steps")
+    ap.add_argument("--mode", choices=["step", "headtohead", "statequant", "multi", "pool"], default="step",
+                    help="step: the benchmark (default).  Side measurements, one JSON object each: headtohead "
+                         "(vLLM's and the reference's kernels beside this library's), statequant (the statequant op "
+                         "per residual format), multi (multi-token call), pool (pool store / load / copy)")
+    ap.add_argument("--batches", type=int, nargs="+", default=None, help="batch sizes of a side measurement")
+    ap.add_argument("--pool-layers", type=int, default=8, help="pools cycled by --mode pool")
     ap.add_argument("--c5-batch", type=int, default=256)
     ap.add_argument("--c5-steps", type=int, default=512)
     return ap.parse_args()
@@ -618,6 +625,276 @@ def run_config5(args):
 
 
 # ---------------------------------------------------------------------------
+# side measurements (--mode): not the headline, one JSON object each
+# ---------------------------------------------------------------------------
+
+def _events_us(call, steps, warmup):
+    """us per call: CUDA events around ``steps`` calls after ``warmup``."""
+    for _ in range(warmup):
+        call()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(steps):
+        call()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / steps * 1e3
+
+
+def _graph_us(fn, reps=10):
+    """us per ``fn()``: ``reps`` calls captured into one CUDA graph, two timed replays."""
+    for _ in range(3):
+        fn()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    graph.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1e3 / (2 * reps)
+
+
+def headtohead(batches=(1, 8, 16, 64, 256), steps=200, warmup=50, seed=0):
+    """Head-to-head against vLLM's own packed-decode kernel and the reference's Triton kernel.
+
+    The comparison of carrykernel's ``modal_vllm_headtohead.py:105-205``: vLLM's
+    ``fused_recurrent_gated_delta_rule_packed_decode`` with an fp32 and with a bf16 state (its
+    serving default) against this library's int8-state step, Qwen-GDN shapes (H = 16 key heads,
+    HV = 32 value heads, K = V = 128), every tensor cast once outside the timed region, CUDA events
+    around ``steps`` calls after ``warmup``.  Added here: the reference's own slot-indexed Triton
+    kernel (from the staged copy, when present) as a third arm on the same GPU; the reference's
+    ``sanity()`` guard (``:94-103``: a bf16 state slower than 1.2x the fp32 one means the harness
+    is suspect and the bf16 ratio is withheld); and a numeric line per batch -- one step of vLLM's
+    fp32-state kernel and of this library from the same dequantised state, fp32 activations and
+    outputs, largest absolute and relative difference of ``out``.  vLLM's kernel and the reference's
+    are comparators only; nothing of either is used by the product."""
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    from oracle import make_ref
+    HH, HHV = 16, 32
+    try:
+        from vllm.model_executor.layers.fla.ops.fused_recurrent import (
+            fused_recurrent_gated_delta_rule_packed_decode as vllm_fn)
+        why = None
+    except Exception as exc:                           # depends on the image
+        vllm_fn, why = None, f"{type(exc).__name__}: {exc}"
+    ref_fn = None
+    if make_ref.ref_path() is not None:
+        sys.path.insert(0, make_ref.ref_path())
+        try:
+            from vllm_integration import quantized_packed_decode as rqpd
+            ref_fn = rqpd.quantized_gated_delta_rule_packed_decode if rqpd.HAS_TRITON else None
+        except Exception:
+            ref_fn = None
+    dev = torch.device("cuda")
+    torch.manual_seed(seed)
+    results = {"H": HH, "HV": HHV, "K": K, "V": V, "steps": steps, "warmup": warmup,
+               "gpu": torch.cuda.get_device_name(0), "suspect": []}
+    if vllm_fn is None:
+        results["vllm"] = f"unavailable: {why}"
+    if ref_fn is None:
+        results["reference_triton"] = "unavailable: oracle/_ref not staged or Triton missing"
+    for B in batches:
+        mixed = torch.randn(B, 2 * HH * K + HHV * V, device=dev)
+        a = torch.randn(B, HHV, device=dev) * 0.5
+        b = torch.randn(B, HHV, device=dev)
+        A_log = torch.randn(HHV, device=dev) * 0.2
+        dt_bias = torch.randn(HHV, device=dev) * 0.1
+        scale = K ** -0.5
+        idx = torch.arange(1, B + 1, dtype=torch.int32, device=dev)
+        h0 = torch.randn(B + 1, HHV, V, K, device=dev) * 0.1
+        row = {}
+        mixed_bf, a_bf, b_bf = mixed.bfloat16(), a.bfloat16(), b.bfloat16()
+        if vllm_fn is not None:
+            for name, state, mx, aa, bb, out_dt in (
+                    ("vllm_fp32_state", h0.clone(), mixed, a, b, torch.float32),
+                    ("vllm_bf16_state", h0.bfloat16(), mixed_bf, a_bf, b_bf, torch.bfloat16)):
+                out = torch.empty(B, 1, HHV, V, device=dev, dtype=out_dt)
+                A_, d_ = (A_log, dt_bias) if out_dt == torch.float32 else (A_log.bfloat16(), dt_bias.bfloat16())
+                call = lambda state=state, mx=mx, aa=aa, bb=bb, out=out, A_=A_, d_=d_: vllm_fn(
+                    mixed_qkv=mx, a=aa, b=bb, A_log=A_, dt_bias=d_, scale=scale, initial_state=state,
+                    out=out, ssm_state_indices=idx, use_qk_l2norm_in_kernel=True)
+                try:
+                    row[name + "_us"] = _events_us(call, steps, warmup)
+                except Exception as exc:
+                    row[name + "_us"] = None
+                    row[name + "_error"] = f"{type(exc).__name__}: {exc}"[:200]
+            t32, tbf = row.get("vllm_fp32_state_us"), row.get("vllm_bf16_state_us")
+            # the reference's guard: half the traffic must not time slower
+            row["bf16_comparison_valid"] = not (t32 and tbf and tbf > 1.2 * t32)
+            if not row["bf16_comparison_valid"]:
+                results["suspect"].append(B)
+        out = torch.empty(B, 1, HHV, V, device=dev, dtype=torch.bfloat16)
+        for fmt, name in ((qpd.RESID_INT8, "ours_int8_resid"), (qpd.RESID_INT4, "ours_int4_resid")):
+            for rscale in ("v", "head"):
+                st = qpd.init_quantized_state(B + 1, HHV, V, K, dev, h0=h0, resid_fmt=fmt, resid_scale=rscale)
+                call = lambda st=st, fmt=fmt: qpd.quantized_gated_delta_rule_packed_decode(
+                    mixed_bf, a_bf, b_bf, A_log, dt_bias, scale, *st, out, idx,
+                    use_qk_l2norm_in_kernel=True, resid_fmt=fmt)
+                row[f"{name}_{rscale}_us"] = _events_us(call, steps, warmup)
+            if ref_fn is not None:
+                st = rqpd.init_quantized_state(B + 1, HHV, V, K, dev, h0=h0, resid_fmt=fmt)
+                call = lambda st=st, fmt=fmt: ref_fn(mixed_bf, a_bf, b_bf, A_log, dt_bias, scale, *st, out, idx,
+                                                     use_qk_l2norm_in_kernel=True, resid_fmt=fmt)
+                row[f"reference_triton_{'int8' if fmt == qpd.RESID_INT8 else 'int4'}_resid_v_us"] = \
+                    _events_us(call, steps, warmup)
+        # numeric line: one step of both kernels from the same dequantised state, fp32 in and out
+        if vllm_fn is not None:
+            st = qpd.init_quantized_state(B + 1, HHV, V, K, dev, h0=h0, resid_fmt=qpd.RESID_INT4, resid_scale="head")
+            h_deq = st[0].float() * st[1][..., None]
+            o_v = torch.empty(B, 1, HHV, V, device=dev)
+            o_o = torch.empty(B, 1, HHV, V, device=dev)
+            vllm_fn(mixed_qkv=mixed, a=a, b=b, A_log=A_log, dt_bias=dt_bias, scale=scale, initial_state=h_deq,
+                    out=o_v, ssm_state_indices=idx, use_qk_l2norm_in_kernel=True)
+            qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, scale, *st, o_o, idx,
+                                                         use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4)
+            torch.cuda.synchronize()
+            row["out_max_abs_diff_vs_vllm_fp32"] = float((o_o - o_v).abs().max())
+            row["out_max_rel_diff_vs_vllm_fp32"] = float(((o_o - o_v).abs() / (o_v.abs() + 1e-4)).max())
+        elems = B * HHV * V * K
+        row["state_traffic_MB"] = {
+            "vllm_fp32": 2 * elems * 4 / 1e6, "vllm_bf16": 2 * elems * 2 / 1e6,
+            "ours_int8_resid": (4 * elems + 4 * B * HHV * V * 4) / 1e6,
+            "ours_int4_resid": (3 * elems + 4 * B * HHV * V * 4) / 1e6}
+        results[f"B{B}"] = row
+    return results
+
+
+def statequant_timing(batches=(8, 64, 256), calls=50):
+    """One fused step through the statequant op (``gdn_quant_step_fused``, [B, HV, K, V] layout, HV = 32,
+    K = V = 128, fp32 q/k/v, 8-bit state) per residual format and residual-scale granularity, the step
+    without error feedback, and the unquantised fp32 step; CUDA events around ``calls`` calls.  The
+    figure includes the op's own work per call (five output allocations, the ctypes call)."""
+    from carrykernel_b200.statequant import kernel as sq
+    dev = torch.device("cuda")
+    cases = ((sq.RES_FP32, "v", "fp32"), (sq.RES_FP16, "v", "fp16"), (sq.RES_FP8, "v", "fp8_e5m2"),
+             (sq.RES_INT8, "v", "int8_per_v"), (sq.RES_INT8, "head", "int8_per_head"),
+             (sq.RES_INT4, "v", "int4_per_v"), (sq.RES_INT4, "head", "int4_per_head"))
+    resid_bytes = {sq.RES_FP32: 4, sq.RES_FP16: 2, sq.RES_FP8: 1, sq.RES_INT8: 1, sq.RES_INT4: 0.5}
+    res = {"HV": HV, "K": K, "V": V, "gpu": torch.cuda.get_device_name(0)}
+
+    def inputs(B):
+        g = torch.Generator().manual_seed(0)
+        h0 = (torch.randn(B, HV, K, V, generator=g) * 0.12).to(dev)
+        q = torch.randn(B, HV, K, generator=g).to(dev)
+        k = (torch.randn(B, HV, K, generator=g) * K ** -0.5).to(dev)
+        v = torch.randn(B, HV, V, generator=g).to(dev)
+        return h0, q, k, v, torch.full((B, HV), 0.98, device=dev), torch.rand(B, HV, generator=g).to(dev)
+
+    for B in batches:
+        row = {}
+        for res_fmt, rs, name in cases:
+            h0, q, k, v, alpha, beta = inputs(B)
+            st = sq.init_quant_state(h0, 8, res_fmt, resid_scale=rs)
+            us = _events_us(lambda: sq.gdn_quant_step_fused(*st, q, k, v, alpha, beta, 8, res_fmt, resid_scale=rs),
+                            calls, 3)
+            row[name] = {"us_per_step": us, "state_GBps": B * HV * K * V * 2 * (1 + resid_bytes[res_fmt]) / us / 1e3}
+        for mode in ("v", "head"):
+            h0, q, k, v, alpha, beta = inputs(B)
+            st = sq.init_quant_state(h0, 8, sq.RES_NONE, state_scale=mode)
+            us = _events_us(lambda: sq.gdn_quant_step_fused(*st, q, k, v, alpha, beta, 8, sq.RES_NONE,
+                                                            state_scale=mode), calls, 3)
+            row[f"no_feedback_scale_per_{mode}"] = {"us_per_step": us, "state_GBps": B * HV * K * V * 2 / us / 1e3}
+        h, q, k, v, alpha, beta = inputs(B)
+        us = _events_us(lambda: sq.gdn_step_fused_fp32(h, q, k, v, alpha, beta), calls, 3)
+        row["fp32_state_unquantised"] = {"us_per_step": us, "state_GBps": B * HV * K * V * 8 / us / 1e3}
+        res[f"B{B}"] = row
+    return res
+
+
+def multi_token_timing(batches=(64, 256), tokens=(2, 4, 8), seed=0):
+    """Time per token of the multi-token call against single-token calls (slot path, int4 residual,
+    per-head scale, bf16), each captured ten times into a CUDA graph."""
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    dev = torch.device("cuda")
+    res = {"H": H, "HV": HV, "K": K, "V": V, "gpu": torch.cuda.get_device_name(0)}
+    for B in batches:
+        for T in tokens:
+            g = torch.Generator().manual_seed(seed)
+            slots = B + 1
+            pool = torch.randn(slots, HV, V, K, generator=g) * 0.12
+            st = [x.to(dev) for x in qpd.init_quantized_state(slots, HV, V, K, "cpu", h0=pool,
+                                                              resid_fmt=qpd.RESID_INT4, resid_scale="head")]
+            mixed = torch.randn(B, T, 2 * H * K + HV * V, generator=g).to(torch.bfloat16).to(dev)
+            a = torch.randn(B, T, HV, generator=g).to(torch.bfloat16).to(dev)
+            b = torch.randn(B, T, HV, generator=g).to(torch.bfloat16).to(dev)
+            A_log = torch.full((HV,), math.log(0.1), device=dev)
+            dt_bias = torch.zeros(HV, device=dev)
+            idx = (torch.randperm(slots - 1, generator=g)[:B] + 1).to(torch.int32).to(dev)
+            out = torch.empty(B, T, HV, V, dtype=torch.bfloat16, device=dev)
+            tmp = torch.empty(B, 1, HV, V, dtype=torch.bfloat16, device=dev)
+            per_tok = [(mixed[:, t].contiguous(), a[:, t].contiguous(), b[:, t].contiguous()) for t in range(T)]
+
+            def single():
+                for m_, a_, b_ in per_tok:
+                    qpd.quantized_gated_delta_rule_packed_decode(m_, a_, b_, A_log, dt_bias, K ** -0.5, *st, tmp, idx,
+                                                                 use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4)
+
+            def multi():
+                qpd.quantized_gated_delta_rule_packed_decode_multi(mixed, a, b, A_log, dt_bias, K ** -0.5, *st, out, idx,
+                                                                   use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4)
+
+            res[f"B{B}_T{T}"] = {"single_token_calls_us_per_token": _graph_us(single) / T,
+                                 "multi_token_call_us_per_token": _graph_us(multi) / T}
+    return res
+
+
+def state_pool_timing(batches=(64, 256), layers=8, seed=0):
+    """Pool store / load / copy kernels: ``layers`` pools cycled so that one pass exceeds the L2, ten
+    passes per CUDA graph.  Bytes per call: store reads the floating-point state and writes the slot,
+    load the reverse, copy reads and writes the quantized slot."""
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    from carrykernel_b200.vllm_integration import state_pool as sp
+    dev = torch.device("cuda")
+    torch.manual_seed(seed)
+    res = {"HV": HV, "K": K, "V": V, "layers": layers, "gpu": torch.cuda.get_device_name(0)}
+    slot_bytes = qpd.state_bytes_per_slot(HV, V, K, True, resid_fmt=qpd.RESID_INT4, resid_scale="head")
+    for B in batches:
+        slots = 2 * B + 1
+        pools = [qpd.init_quantized_state(slots, HV, V, K, dev, resid_fmt=qpd.RESID_INT4, resid_scale="head")
+                 for _ in range(layers)]
+        idx = (torch.randperm(B, device=dev) + 1).to(torch.int32)
+        idx2 = idx + B
+        row = {}
+        for name, dtype, es in (("fp32", torch.float32, 4), ("bf16", torch.bfloat16, 2)):
+            hs = [(torch.randn(B, HV, V, K, device=dev) * 0.1).to(dtype) for _ in range(layers)]
+
+            def store(keep):
+                for h, pool in zip(hs, pools):
+                    sp.store_state(h, pool, idx, resid_fmt=qpd.RESID_INT4, keep_error=keep)
+
+            def load():
+                for h, pool in zip(hs, pools):
+                    sp.load_state(pool, idx, out=h, resid_fmt=qpd.RESID_INT4)
+
+            bytes_call = B * (HV * V * K * es + slot_bytes)
+            for label, fn in ((f"store_{name}", lambda: store(False)),
+                              (f"store_{name}_keep_error", lambda: store(True)), (f"load_{name}", load)):
+                us = _graph_us(fn) / layers
+                row[label] = {"us_per_call": us, "GB_per_s": bytes_call / us / 1e3}
+            del hs
+
+        def copy():
+            for pool in pools:
+                sp.copy_slots(pool, idx, idx2, resid_fmt=qpd.RESID_INT4)
+
+        us = _graph_us(copy) / layers
+        row["copy"] = {"us_per_call": us, "GB_per_s": 2 * B * slot_bytes / us / 1e3}
+        res[f"B{B}"] = row
+    return res
+
+
+SIDE_MODES = {"headtohead": headtohead, "statequant": statequant_timing, "multi": multi_token_timing,
+              "pool": state_pool_timing}
+
+
+# ---------------------------------------------------------------------------
 # main
 # ---------------------------------------------------------------------------
 
@@ -727,6 +1004,15 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    if args.mode != "step":
+        if rank == 0:
+            kw = {} if args.batches is None else {"batches": tuple(args.batches)}
+            if args.mode == "pool":
+                kw["layers"] = args.pool_layers
+            if args.mode == "headtohead":
+                kw.update(steps=max(args.steps, 1) * 10, warmup=max(args.warmup, 3) * 10)
+            print(json.dumps(SIDE_MODES[args.mode](**kw)))
+        return
     if args.config == 5:
         if rank == 0:
             run_config5(args)
