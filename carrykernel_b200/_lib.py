@@ -190,5 +190,43 @@ def require_cuda(t: torch.Tensor, name: str):
             f"{name} is on {t.device}: this op has no CPU path, move the tensors to a CUDA device")
 
 
+def same_device(device, **tensors):
+    """Every tensor handed to a kernel must live on the state's device: the kernels take raw
+    addresses, so a CPU tensor or one of another GPU would be a wild pointer on the device."""
+    for name, t in tensors.items():
+        if t is not None and t.device != device:
+            raise ValueError(f"{name} is on {t.device} but the state is on {device}: all tensors of a call "
+                             "must be on the same CUDA device")
+
+
+def need_shape(t: torch.Tensor, shape, name: str):
+    if tuple(t.shape) != tuple(shape):
+        raise ValueError(f"{name} must be {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def status_ptr(status, device):
+    """Address of the optional device status word: an int32 tensor of one element on the state's
+    device that the kernels OR their status bits into (``STATUS_BAD_SLOT``: a slot id beyond the pool
+    was treated as padding; ``STATUS_TIMEOUT``: a wait on data in flight ran out and the affected
+    tiles were left untouched).  The caller zeroes it and reads it when convenient
+    (:func:`raise_for_status`); the calls themselves never read it back."""
+    if status is None:
+        return None
+    if status.dtype != torch.int32 or status.numel() != 1:
+        raise ValueError("status must be an int32 tensor of one element")
+    same_device(device, status=status)
+    return status.data_ptr()
+
+
+def raise_for_status(status: torch.Tensor, what: str = "carry_gdn"):
+    """Read the status word (this synchronises with the device) and raise if a bit is set."""
+    bits = int(status.item())
+    if bits:
+        names = [n for b, n in ((STATUS_BAD_SLOT, "slot id beyond the pool (treated as padding)"),
+                                (STATUS_TIMEOUT, "a wait on data in flight ran out (tiles left untouched)"))
+                 if bits & b]
+        raise RuntimeError(f"{what}: device status {bits}: " + "; ".join(names))
+
+
 def current_stream_ptr(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream

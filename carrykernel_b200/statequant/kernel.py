@@ -127,15 +127,38 @@ def _activation(t: torch.Tensor) -> torch.Tensor:
     return t if t.dtype in (torch.float32, torch.bfloat16, torch.float16) else t.float()
 
 
+def _check_step_tensors(h_int8, scale, e, e_scale, q, k, v, alpha, beta, res_fmt, resid_scale, state_scale):
+    """Device and shape of everything one step reads: the kernels take raw addresses."""
+    B, HV, K, V = h_int8.shape
+    dev = h_int8.device
+    _lib.same_device(dev, scale=scale, e=e, e_scale=e_scale, q=q, k=k, v=v, alpha=alpha, beta=beta)
+    _lib.need_shape(scale, (B, HV, V) if state_scale == "v" else (B, HV), "scale")
+    _lib.need_shape(q, (B, HV, K), "q")
+    _lib.need_shape(k, (B, HV, K), "k")
+    _lib.need_shape(v, (B, HV, V), "v")
+    _lib.need_shape(alpha, (B, HV), "alpha")
+    _lib.need_shape(beta, (B, HV), "beta")
+    if e is not None:
+        _lib.need_shape(e, (B, HV, K, V // 2 if res_fmt == RES_INT4 else V), "e")
+    if e_scale is not None:
+        _lib.need_shape(e_scale, (B, HV, V) if resid_scale == "v" else (B, HV), "e_scale")
+
+
 def quant_step_into(h_int8, scale, e, e_scale, q, k, v, alpha, beta, outputs,
                     bits: int = 8, res_fmt: int = RES_FP32, resid_scale: str = "v",
-                    state_scale: str = "v"):
+                    state_scale: str = "v", status=None):
     """Launch one step into caller-provided ``outputs = (o, h_out, scale_out,
     e_out, e_scale_out)``; no allocation, no synchronisation.  Output state
     buffers may be the input buffers (in-place).  This is the low-level entry
-    the wrappers and the benchmark share."""
+    the wrappers and the benchmark share.  ``status``: optional int32 device
+    word for the kernel's status bits (``_lib.status_ptr``)."""
     o, h_out, scale_out, e_out, e_scale_out = outputs
     B, HV, K, V = h_int8.shape
+    _check_step_tensors(h_int8, scale, e, e_scale, q, k, v, alpha, beta, res_fmt, resid_scale, state_scale)
+    _lib.same_device(h_int8.device, o=o, h_out=h_out, scale_out=scale_out, e_out=e_out, e_scale_out=e_scale_out)
+    _lib.need_shape(o, (B, HV, V), "o")
+    _lib.need_shape(h_out, h_int8.shape, "h_out")
+    _lib.need_shape(scale_out, scale.shape, "scale_out")
     a = _lib.StepArgs()
     a.h_in, a.scale_in, a.e_in, a.e_scale_in = h_int8.data_ptr(), scale.data_ptr(), _lib.ptr(e), _lib.ptr(e_scale)
     a.q, a.k, a.v = q.data_ptr(), k.data_ptr(), v.data_ptr()
@@ -149,7 +172,7 @@ def quant_step_into(h_int8, scale, e, e_scale, q, k, v, alpha, beta, outputs,
     a.resid_scale_mode = _scale_mode(resid_scale)
     a.state_scale_mode = _scale_mode(state_scale)
     a.eps_mode = _lib.EPS_ON_AMAX
-    a.status = None
+    a.status = _lib.status_ptr(status, h_int8.device)
     lib = _lib.load_library()
     with torch.cuda.device(h_int8.device):
         rc = lib.carry_gdn_quant_step(a, _lib.current_stream_ptr(h_int8.device))
@@ -168,6 +191,10 @@ def gdn_quant_step_fused(h_int8, scale, e, e_scale, q, k, v, alpha, beta,
     """
     assert h_int8.dtype == torch.int8, f"h_int8 must be int8, got {h_int8.dtype}"
     assert h_int8.dim() == 4, f"expected [B, HV, K, V], got {tuple(h_int8.shape)}"
+    _scale_mode(resid_scale), _scale_mode(state_scale)
+    _check_step_tensors(h_int8, scale, None if res_fmt == RES_NONE else e,
+                        e_scale if res_fmt in (RES_INT8, RES_INT4) else None, q, k, v, alpha, beta,
+                        res_fmt, resid_scale, state_scale)
     _lib.require_cuda(h_int8, "h_int8")
     B, HV, K, V = h_int8.shape
     dev = h_int8.device
@@ -213,9 +240,15 @@ def gdn_quant_step_fused(h_int8, scale, e, e_scale, q, k, v, alpha, beta,
 def gdn_step_fused_fp32(h, q, k, v, alpha, beta, BLOCK_V: int = 32):
     """Fused fp32 GDN step (no quantisation).  Returns ``(h_out, o)``."""
     assert h.dim() == 4, f"expected [B, HV, K, V], got {tuple(h.shape)}"
-    _lib.require_cuda(h, "h")
     B, HV, K, V = h.shape
     dev = h.device
+    _lib.same_device(dev, q=q, k=k, v=v, alpha=alpha, beta=beta)
+    _lib.need_shape(q, (B, HV, K), "q")
+    _lib.need_shape(k, (B, HV, K), "k")
+    _lib.need_shape(v, (B, HV, V), "v")
+    _lib.need_shape(alpha, (B, HV), "alpha")
+    _lib.need_shape(beta, (B, HV), "beta")
+    _lib.require_cuda(h, "h")
     h = h.contiguous().float()
     q, k, v = _activation(q), _activation(k), _activation(v)
     if not (q.dtype == k.dtype == v.dtype):

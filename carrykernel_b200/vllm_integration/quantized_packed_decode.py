@@ -20,6 +20,12 @@ head instead of one per V-row; the granularity is read off the shape.
 
 The call allocates nothing, never synchronises and reads nothing back to the
 host, so it can be captured in a CUDA graph.  There is no CPU path.
+
+Deviations from the reference's contract, both stricter: ``a`` and ``b`` must
+share one dtype (the reference loads each through its own pointer type), and
+``A_log`` / ``dt_bias`` must be contiguous (the call does not copy them).  Every
+tensor must be on the pool's device and is checked for the shape the kernel
+will index; a violation raises ``ValueError`` before anything is launched.
 """
 
 from __future__ import annotations
@@ -42,7 +48,7 @@ _RES_ID = {RESID_INT8: _lib.RES_INT8, RESID_INT4: _lib.RES_INT4}
 
 
 def _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scale, resid_codes, resid_scale,
-                 out, out_shape_of, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt):
+                 out, out_shape_of, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt, status=None):
     """Validation shared by the single- and the multi-token call (the reference's conditions,
     ``vllm_integration/quantized_packed_decode.py:268-307``) and the filled argument block.
     ``mixed_qkv``, ``a``, ``b`` are the 2-D views of one token per request."""
@@ -87,7 +93,6 @@ def _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scal
     if resid_fmt == RESID_INT4 and K % 2 != 0:
         raise ValueError(f"int4 residual packing needs an even K, got {K}")
 
-    _lib.require_cuda(state_codes, "state_codes")
     if resid_scale.dim() == 3:
         rmode = _lib.SCALE_PER_V
     elif resid_scale.dim() == 2:
@@ -105,8 +110,26 @@ def _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scal
         raise ValueError("resid_scale must be fp32 and dense within a slot")
     if a.stride(-1) != 1 or b.stride(-1) != 1 or a.dtype != b.dtype:
         raise ValueError("a and b must share a dtype and be contiguous in their last dimension")
-    A_log = A_log.contiguous()
-    dt_bias = dt_bias.contiguous()
+    # The kernels take raw addresses: everything has to be on the pool's device and large enough for what
+    # B, HV, V, K and the slot count make the kernel index.
+    dev = state_codes.device
+    _lib.same_device(dev, mixed_qkv=mixed_qkv, a=a, b=b, A_log=A_log, dt_bias=dt_bias, state_scale=state_scale,
+                     resid_codes=resid_codes, resid_scale=resid_scale, out=out, ssm_state_indices=ssm_state_indices)
+    if a.dim() != 2 or b.dim() != 2:
+        raise ValueError("a and b must be 2-D: [B, HV]")
+    _lib.need_shape(a, (B, HV), "a")
+    _lib.need_shape(b, (B, HV), "b")
+    _lib.need_shape(A_log, (HV,), "A_log")
+    _lib.need_shape(dt_bias, (HV,), "dt_bias")
+    if not A_log.is_contiguous() or not dt_bias.is_contiguous():
+        raise ValueError("A_log and dt_bias must be contiguous")
+    _lib.need_shape(ssm_state_indices, (B,), "ssm_state_indices")
+    _lib.need_shape(state_scale, (num_slots, HV, V), "state_scale")
+    _lib.need_shape(resid_scale, (num_slots, HV, V) if rmode == _lib.SCALE_PER_V else (num_slots, HV), "resid_scale")
+    if resid_codes.shape[:3] != (num_slots, HV, V):
+        raise ValueError(f"resid_codes must be [{num_slots}, {HV}, {V}, ..], got {tuple(resid_codes.shape)}")
+    status_addr = _lib.status_ptr(status, dev)
+    _lib.require_cuda(state_codes, "state_codes")
 
     args = _lib.PackedArgs()
     args.mixed_qkv, args.stride_mixed_tok, args.qkv_dtype = mixed_qkv.data_ptr(), mixed_qkv.stride(0), _lib.dtype_id(mixed_qkv)
@@ -129,8 +152,8 @@ def _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scal
     args.resid_scale_mode = rmode
     args.eps_mode = _lib.EPS_ON_SCALE
     args.qmax = QMAX_INT8
-    args.status = None
-    return args, (A_log, dt_bias)       # the contiguous copies must outlive the launch call
+    args.status = status_addr
+    return args, None
 
 
 def quantized_gated_delta_rule_packed_decode(
@@ -148,11 +171,17 @@ def quantized_gated_delta_rule_packed_decode(
     ssm_state_indices: torch.Tensor,
     use_qk_l2norm_in_kernel: bool = False,
     resid_fmt: int = RESID_INT8,
+    status: torch.Tensor | None = None,
 ):
-    """Advance every request's slot by one token, in place; returns ``out``."""
+    """Advance every request's slot by one token, in place; returns ``out``.
+
+    ``status`` (additive, optional): an int32 tensor of one element on the pool's device that the
+    kernel ORs its status bits into -- a slot id beyond the pool (that request is treated as padding:
+    zeros to ``out``, pool untouched) or a wait that ran out.  Without it such a request is silently a
+    padding request.  See ``_lib.raise_for_status``."""
     args, _keep = _packed_args(mixed_qkv, a, b, A_log, dt_bias, scale, state_codes, state_scale, resid_codes,
                                resid_scale, out, lambda B, HV, V: (B, 1, HV, V), ssm_state_indices,
-                               use_qk_l2norm_in_kernel, resid_fmt)
+                               use_qk_l2norm_in_kernel, resid_fmt, status)
     lib = _lib.load_library()
     dev = state_codes.device
     with torch.cuda.device(dev):
@@ -176,6 +205,7 @@ def quantized_gated_delta_rule_packed_decode_multi(
     ssm_state_indices: torch.Tensor,
     use_qk_l2norm_in_kernel: bool = False,
     resid_fmt: int = RESID_INT8,
+    status: torch.Tensor | None = None,
 ):
     """Advance every request's slot by T tokens in one call, in place; returns ``out``.
 
@@ -184,7 +214,9 @@ def quantized_gated_delta_rule_packed_decode_multi(
     that of T single-token calls on ``mixed_qkv[:, t]`` in turn, bit for bit; the
     state tile of a request stays on chip between its tokens.  (No counterpart in
     carrykernel: this is the multi-token decode vLLM reaches through its
-    speculative-decoding path.)"""
+    speculative-decoding path.)  Shapes the streaming kernels do not take (K or V other than
+    128, ...) fall back to one single-token call per token, which allocates a ``[B, 1, HV, V]``
+    scratch block: that path is not CUDA-graph capturable.  ``status`` as in the single-token call."""
     if mixed_qkv.dim() != 3 or a.dim() != 3 or b.dim() != 3:
         raise ValueError("mixed_qkv, a and b must be 3-D: [B, T, ...]")
     B, T = mixed_qkv.shape[0], mixed_qkv.shape[1]
@@ -192,7 +224,7 @@ def quantized_gated_delta_rule_packed_decode_multi(
         raise ValueError("mixed_qkv, a and b must agree on [B, T]")
     step, _keep = _packed_args(mixed_qkv[:, 0], a[:, 0], b[:, 0], A_log, dt_bias, scale, state_codes, state_scale,
                                resid_codes, resid_scale, out, lambda B_, HV, V: (B_, T, HV, V), ssm_state_indices,
-                               use_qk_l2norm_in_kernel, resid_fmt)
+                               use_qk_l2norm_in_kernel, resid_fmt, status)
     args = _lib.PackedMultiArgs()
     args.step = step
     args.T = T
@@ -208,7 +240,7 @@ def quantized_gated_delta_rule_packed_decode_multi(
         for t in range(T):
             quantized_gated_delta_rule_packed_decode(
                 mixed_qkv[:, t], a[:, t], b[:, t], A_log, dt_bias, scale, state_codes, state_scale, resid_codes,
-                resid_scale, tmp, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt)
+                resid_scale, tmp, ssm_state_indices, use_qk_l2norm_in_kernel, resid_fmt, status)
             out[:, t:t + 1].copy_(tmp)
         return out
     _lib.check(rc, "carry_gdn_packed_decode_multi")

@@ -18,6 +18,10 @@ synchronisation, CUDA-graph capturable:
 * :func:`copy_slots` -- whole slots, residual included, bit for bit, within a
   pool or into a second pool (spill pool, checkpoint, prefix-cache entry).
 
+Every function takes an optional ``status``: an int32 device word the kernel ORs
+its status bits into (a slot id beyond the pool is skipped and flagged there;
+see ``_lib.status_ptr``).
+
 A *pool* is the 4-tuple ``(state_codes, state_scale, resid_codes, resid_scale)``
 that ``init_quantized_state`` returns.  There is no CPU path.
 """
@@ -63,6 +67,10 @@ def _pool_struct(pool, resid_fmt):
         raise ValueError("resid_scale must be fp32 and dense within a slot")
     if any(t.device != state_codes.device for t in (state_scale, resid_codes, resid_scale)):
         raise ValueError("the four pool tensors must live on one device")
+    _lib.need_shape(state_scale, (num_slots, HV, V), "state_scale")
+    _lib.need_shape(resid_scale, (num_slots, HV, V) if rmode == _lib.SCALE_PER_V else (num_slots, HV), "resid_scale")
+    if resid_codes.shape[:3] != (num_slots, HV, V):
+        raise ValueError(f"resid_codes must be [{num_slots}, {HV}, {V}, ..], got {tuple(resid_codes.shape)}")
     p = _lib.Pool()
     p.state_codes, p.state_scale = state_codes.data_ptr(), state_scale.data_ptr()
     p.resid_codes, p.resid_scale = resid_codes.data_ptr(), resid_scale.data_ptr()
@@ -93,7 +101,7 @@ def _state_tensor(h, B, HV, V, K, device, name):
     return h.data_ptr(), h.stride(0), _lib.dtype_id(h)
 
 
-def store_state(h, pool, ssm_state_indices, resid_fmt: int = RESID_INT8, keep_error: bool = False):
+def store_state(h, pool, ssm_state_indices, resid_fmt: int = RESID_INT8, keep_error: bool = False, status=None):
     """Quantise ``h [B, HV, V, K]`` (fp32, bf16 or fp16) into slots
     ``ssm_state_indices [B]`` of ``pool``.  Slot ids ``<= 0`` are skipped."""
     p = _pool_struct(pool, resid_fmt)
@@ -105,7 +113,7 @@ def store_state(h, pool, ssm_state_indices, resid_fmt: int = RESID_INT8, keep_er
     args.h, args.stride_h_req, args.h_dtype = _state_tensor(h, args.B, p.HV, p.V, p.K, dev, "h")
     args.keep_error = int(bool(keep_error))
     args.qmax = QMAX_INT8
-    args.status = None
+    args.status = _lib.status_ptr(status, dev)
     lib = _lib.load_library()
     with torch.cuda.device(dev):
         rc = lib.carry_gdn_pool_store(args, _lib.current_stream_ptr(dev))
@@ -113,7 +121,7 @@ def store_state(h, pool, ssm_state_indices, resid_fmt: int = RESID_INT8, keep_er
 
 
 def load_state(pool, ssm_state_indices, out=None, dtype=torch.float32, resid_fmt: int = RESID_INT8,
-               with_residual: bool = True):
+               with_residual: bool = True, status=None):
     """``out[n] = codes * scale (+ resid_codes * resid_scale)`` of slot
     ``ssm_state_indices[n]``; zeros for slot ids ``<= 0``.  ``out`` is allocated
     (``dtype``) when not given.  Returns ``out [B, HV, V, K]``."""
@@ -128,7 +136,7 @@ def load_state(pool, ssm_state_indices, out=None, dtype=torch.float32, resid_fmt
     args.B = B
     args.h, args.stride_h_req, args.h_dtype = _state_tensor(out, B, p.HV, p.V, p.K, dev, "out")
     args.with_residual = int(bool(with_residual))
-    args.status = None
+    args.status = _lib.status_ptr(status, dev)
     lib = _lib.load_library()
     with torch.cuda.device(dev):
         rc = lib.carry_gdn_pool_load(args, _lib.current_stream_ptr(dev))
@@ -136,7 +144,7 @@ def load_state(pool, ssm_state_indices, out=None, dtype=torch.float32, resid_fmt
     return out
 
 
-def copy_slots(src_pool, src_indices, dst_indices, dst_pool=None, resid_fmt: int = RESID_INT8):
+def copy_slots(src_pool, src_indices, dst_indices, dst_pool=None, resid_fmt: int = RESID_INT8, status=None):
     """Copy slot ``src_indices[n]`` of ``src_pool`` to slot ``dst_indices[n]`` of
     ``dst_pool`` (default: the same pool), all four tensors, bit for bit.  Pairs
     with an id ``<= 0`` are skipped; no destination may also be a source or a
@@ -156,7 +164,7 @@ def copy_slots(src_pool, src_indices, dst_indices, dst_pool=None, resid_fmt: int
     args.src_slots, args.stride_src_slots = _indices(src_indices, "src_indices", dev)
     args.dst_slots, args.stride_dst_slots = _indices(dst_indices, "dst_indices", dev)
     args.B = src_indices.shape[0]
-    args.status = None
+    args.status = _lib.status_ptr(status, dev)
     lib = _lib.load_library()
     with torch.cuda.device(dev):
         rc = lib.carry_gdn_pool_copy(args, _lib.current_stream_ptr(dev))

@@ -2,7 +2,8 @@
 
 Usage (only where a checkout of tomalmog/carrykernel is available):
 
-    python tests/golden/make_golden.py /path/to/carrykernel
+    python tests/golden/make_golden.py /path/to/carrykernel            # every fixture
+    python tests/golden/make_golden.py /path/to/carrykernel config1    # only the full-size config-1 run
 
 It imports the reference's own CPU code (statequant/reference.py,
 statequant/quant.py, statequant/kernel.py, the helper oracle in
@@ -68,7 +69,34 @@ def kernel_test_inputs(T, B, HV, K, V, seed):
     return h0, q, k, v, alpha, beta
 
 
-def main(ref_root):
+def config1(rr, rq):
+    """BASELINE config 1 at its stated size: batch 1, 4 heads, K = V = 128, T = 2000 sequential decode
+    steps, constant decay 0.995, q and k ~ N(0,1) L2-normalised per head, v ~ N(0,1),
+    beta = sigmoid(N(0,1)), seed 0, draw order of experiments/exp2b_granularity.py:49-56; int8 state
+    with one scale per V column and an fp32 error-feedback residual against the unquantised fp32
+    recurrence.  Stored: both final states, the relative L2 error, and sums of the inputs so that a
+    test can tell its own draws are the same ones."""
+    torch.manual_seed(0)
+    HV, K, V, T = 4, 128, 128, 2000
+    q = torch.randn(T, HV, K); q = q / q.norm(dim=-1, keepdim=True).clamp(min=1e-8)
+    k = torch.randn(T, HV, K); k = k / k.norm(dim=-1, keepdim=True).clamp(min=1e-8)
+    v = torch.randn(T, HV, V)
+    alpha = torch.full((T, HV), 0.995)
+    beta = torch.randn(T, HV).sigmoid()
+    h0 = torch.randn(HV, K, V) * 0.1
+    _, h_ref = rr.gdn_decode_batched(h0, q, k, v, alpha, beta)
+    h = h0.clone()
+    fb = rq.ErrorFeedback(h0.shape)
+    for t in range(T):
+        h, _ = rr.gdn_step_batched(h, q[t], k[t], v[t], alpha[t], beta[t])
+        h = fb.step(h, lambda x: rq.per_axis_quantize(x, 8, -2))
+    err = ((h - h_ref).norm() / h_ref.norm()).item()
+    print(f"  config 1: final-state relative L2 error {err:.4e}")
+    sums = torch.tensor([x.double().sum().item() for x in (q, k, v, beta, h0)], dtype=torch.float64)
+    save("config1_mechanism", h_ref=h_ref, h_quant=h, err=err, input_sums=sums)
+
+
+def main(ref_root, only=None):
     sys.path.insert(0, ref_root)
     from statequant import kernel as tk
     from statequant import quant as rq
@@ -78,6 +106,10 @@ def main(ref_root):
     mr = load_residual_quantizers(ref_root)
 
     torch.set_num_threads(1)   # reduction order must not depend on the host
+    if only in (None, "config1"):
+        config1(rr, rq)
+    if only is not None:
+        return
 
     # -- 1. quantizers ------------------------------------------------------
     torch.manual_seed(11)
@@ -194,6 +226,6 @@ def main(ref_root):
 
 
 if __name__ == "__main__":
-    if len(sys.argv) != 2:
+    if len(sys.argv) not in (2, 3):
         raise SystemExit(__doc__)
-    main(sys.argv[1])
+    main(sys.argv[1], sys.argv[2] if len(sys.argv) == 3 else None)

@@ -73,6 +73,25 @@ def make_packed_inputs(B, H, HV, K, V, seed, dtype=torch.float32, qk_gain=1.0):
     return mixed.to(dtype), a.to(dtype), b.to(dtype), A_log, dt_bias
 
 
+def config1_inputs():
+    """BASELINE config 1: batch 1, 4 heads, K = V = 128, T = 2000, constant decay 0.995, q and k
+    ~ N(0,1) L2-normalised per head, v ~ N(0,1), beta = sigmoid(N(0,1)), ``torch.manual_seed(0)``,
+    drawn in the order of the reference's experiments/exp2b_granularity.py:49-56 (the same draws as
+    ``tests/golden/make_golden.py:config1``).  Returns ``(h0, q, k, v, alpha, beta, input_sums)``."""
+    state = torch.random.get_rng_state()
+    torch.manual_seed(0)
+    HV, K, V, T = 4, 128, 128, 2000
+    q = torch.randn(T, HV, K); q = q / q.norm(dim=-1, keepdim=True).clamp(min=1e-8)
+    k = torch.randn(T, HV, K); k = k / k.norm(dim=-1, keepdim=True).clamp(min=1e-8)
+    v = torch.randn(T, HV, V)
+    alpha = torch.full((T, HV), 0.995)
+    beta = torch.randn(T, HV).sigmoid()
+    h0 = torch.randn(HV, K, V) * 0.1
+    torch.random.set_rng_state(state)
+    sums = torch.tensor([x.double().sum().item() for x in (q, k, v, beta, h0)], dtype=torch.float64)
+    return h0, q, k, v, alpha, beta, sums
+
+
 def code_flips(got: torch.Tensor, ref: torch.Tensor):
     """Returns ``(mask_of_differing, fraction, max_abs_diff)`` for integer codes."""
     d = (got.to(torch.int32) - ref.to(torch.int32)).abs()

@@ -242,3 +242,49 @@ def test_out_of_range_slot_is_flagged_not_followed():
     torch.cuda.synchronize()
     assert int(status.item()) & _lib.STATUS_BAD_SLOT
     assert torch.all(out == 0)
+
+
+@pytest.mark.parametrize("K", [128, 64])
+def test_status_word_through_the_public_calls(K):
+    """An out-of-range slot id shows up in the optional ``status`` tensor of the Python surfaces (the
+    streaming kernel at K = V = 128, the generic one otherwise), for the decode step, the multi-token
+    call and the pool calls; ``raise_for_status`` turns it into an exception."""
+    qpd = _qpd()
+    from carrykernel_b200 import _lib
+    from carrykernel_b200.vllm_integration import state_pool
+    H, HV, V, num_slots = 2, 4, K, 4
+    st = [x.to(DEV) for x in qpd.init_quantized_state(num_slots, HV, V, K, "cpu", resid_fmt=qpd.RESID_INT4,
+                                                      resid_scale="head")]
+    before = [x.clone() for x in st]
+    mixed, a, b, A_log, dt_bias = [x.to(DEV) for x in make_packed_inputs(2, H, HV, K, V, seed=5)]
+    idx = torch.tensor([2, num_slots + 3], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.full((2, 1, HV, V), float("nan"), device=DEV)
+    qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, K ** -0.5, *st, out, idx,
+                                                 use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4, status=status)
+    assert int(status.item()) == _lib.STATUS_BAD_SLOT
+    assert torch.all(out[1] == 0) and not torch.isnan(out[0]).any()
+    for x, y in zip(st, before):
+        assert torch.equal(x[[0, 1, 3]], y[[0, 1, 3]])
+    with pytest.raises(RuntimeError, match="slot id beyond the pool"):
+        _lib.raise_for_status(status, "decode step")
+    # a clean call leaves the word alone
+    status.zero_()
+    qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, K ** -0.5, *st, out,
+                                                 torch.tensor([1, 0], dtype=torch.int32, device=DEV),
+                                                 use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4, status=status)
+    _lib.raise_for_status(status)
+    # multi-token call
+    out_m = torch.empty(2, 2, HV, V, device=DEV)
+    qpd.quantized_gated_delta_rule_packed_decode_multi(
+        torch.stack([mixed, mixed], 1), torch.stack([a, a], 1), torch.stack([b, b], 1), A_log, dt_bias, K ** -0.5,
+        *st, out_m, idx, use_qk_l2norm_in_kernel=True, resid_fmt=qpd.RESID_INT4, status=status)
+    assert int(status.item()) == _lib.STATUS_BAD_SLOT and torch.all(out_m[1] == 0)
+    # pool calls
+    for fn in (lambda s: state_pool.store_state(torch.zeros(2, HV, V, K, device=DEV), st, idx, qpd.RESID_INT4, status=s),
+               lambda s: state_pool.load_state(st, idx, resid_fmt=qpd.RESID_INT4, status=s),
+               lambda s: state_pool.copy_slots(st, torch.tensor([1, 1], dtype=torch.int32, device=DEV), idx,
+                                               resid_fmt=qpd.RESID_INT4, status=s)):
+        status.zero_()
+        fn(status)
+        assert int(status.item()) == _lib.STATUS_BAD_SLOT

@@ -180,6 +180,33 @@ def test_inputs_untouched_and_e_scale_none():
     assert out[4] is None
 
 
+@pytest.mark.parametrize("shape", [(3, 4, 128, 128), (2, 3, 64, 48)])
+@pytest.mark.parametrize("res_fmt,resid_scale", [(0, "v"), (1, "v"), (2, "v"), (3, "v"), (3, "head"), (4, "v"), (4, "head")])
+def test_in_place_equals_out_of_place(shape, res_fmt, resid_scale):
+    """The C ABI allows every output state buffer to be its input buffer (include/carry_gdn.h): the step
+    run in place must leave exactly what the out-of-place call returns, for every residual format, on the
+    streaming kernel (128 x 128) and on the generic one."""
+    sq, binding = _mods()
+    B, HV, K, V = shape
+    h0, q, k, v, alpha, beta = seeded_inputs(B, HV, K, V, seed=31, alpha_mode="gated")
+    st = list(_to_dev(orc.init_quant_state(h0, 8, res_fmt, resid_scale)))
+    acts = _to_dev([q, k, v, alpha, beta])
+    for _ in range(2):                                  # the second step starts from a non-zero residual
+        ref = sq.gdn_quant_step_fused(*st, *acts, bits=8, res_fmt=res_fmt, resid_scale=resid_scale)
+        inplace = [None if x is None else x.clone() for x in st]
+        o = torch.full((B, HV, V), float("nan"), device=DEV)
+        sq.quant_step_into(*inplace, *acts, (o, *inplace), 8, res_fmt, resid_scale)
+        torch.cuda.synchronize()
+        assert torch.equal(o, ref[0])
+        for got, want, name in zip(inplace, ref[1:], ("codes", "scale", "residual", "residual scale")):
+            if want is None:
+                continue
+            same = torch.equal(got.view(torch.uint8), want.view(torch.uint8)) if got.dtype == torch.float8_e5m2 \
+                else torch.equal(got, want)
+            assert same, f"in place: {name} differ (format {res_fmt}, {resid_scale})"
+        st = list(ref[1:])
+
+
 def test_zero_state_and_empty_batch():
     sq, binding = _mods()
     K = V = 128

@@ -119,10 +119,12 @@ def test_reference_signatures_are_kept():
         ["h", "q", "k", "v", "alpha", "beta", "BLOCK_V"]
     assert list(inspect.signature(binding.gdn_quant_decode_cuda).parameters)[:10] == \
         ["h0", "q", "k", "v", "alpha", "beta", "T", "bits", "res_fmt", "BLOCK_V"]
-    assert list(inspect.signature(qpd.quantized_gated_delta_rule_packed_decode).parameters) == [
+    ps = inspect.signature(qpd.quantized_gated_delta_rule_packed_decode).parameters
+    assert list(ps)[:14] == [
         "mixed_qkv", "a", "b", "A_log", "dt_bias", "scale", "state_codes", "state_scale",
         "resid_codes", "resid_scale", "out", "ssm_state_indices", "use_qk_l2norm_in_kernel",
         "resid_fmt"]
+    assert list(ps)[14:] == ["status"] and ps["status"].default is None      # additive, optional
     assert (sq.RES_FP32, sq.RES_FP16, sq.RES_FP8, sq.RES_INT8) == (0, 1, 2, 3)
     assert (qpd.RESID_INT8, qpd.RESID_INT4, qpd.NULL_BLOCK_ID) == (0, 1, 0)
     assert issubclass(binding.CudaUnavailable, RuntimeError)
@@ -241,8 +243,61 @@ def test_packed_decode_validation_messages():
         call(out=out[:, :, :2])
     with pytest.raises(ValueError, match="cannot infer H"):
         call(mixed_qkv=torch.zeros(B, HV * V + 3))
+    # sizes the kernel would index past, and tensors that are not on the pool's device: rejected
+    # before anything is launched (the kernels take raw addresses)
+    with pytest.raises(ValueError, match=r"a must be \(2, 4\)"):
+        call(a=torch.zeros(B, HV - 1))
+    with pytest.raises(ValueError, match=r"b must be \(2, 4\)"):
+        call(b=torch.zeros(B + 1, HV))
+    with pytest.raises(ValueError, match="A_log must be"):
+        call(A_log=torch.zeros(HV + 1))
+    with pytest.raises(ValueError, match="dt_bias must be"):
+        call(dt_bias=torch.zeros(1))
+    with pytest.raises(ValueError, match="contiguous"):
+        call(A_log=torch.zeros(2 * HV)[::2])
+    with pytest.raises(ValueError, match="ssm_state_indices must be"):
+        call(ssm_state_indices=idx[:1])
+    with pytest.raises(ValueError, match="state_scale must be"):
+        call(state_scale=ss[:2])
+    with pytest.raises(ValueError, match="resid_scale must be"):
+        call(resid_scale=rs[:, :2])
+    rc4 = qpd.init_quantized_state(2, HV, V, K, "cpu", resid_fmt=qpd.RESID_INT4)[2]
+    with pytest.raises(ValueError, match="resid_codes must be"):
+        call(resid_codes=rc4, resid_fmt=qpd.RESID_INT4)        # a residual pool of fewer slots than the state's
+    with pytest.raises(ValueError, match="share a dtype"):
+        call(a=a.bfloat16())
+    with pytest.raises(ValueError, match="ssm_state_indices is on meta"):
+        call(ssm_state_indices=torch.zeros(B, dtype=torch.int32, device="meta"))
+    with pytest.raises(ValueError, match="mixed_qkv is on meta"):
+        call(mixed_qkv=torch.zeros(mixed.shape, device="meta"))
+    with pytest.raises(ValueError, match="status must be an int32"):
+        call(status=torch.zeros(1))
     with pytest.raises(qpd.CudaUnavailable):
         call()
+
+
+def test_statequant_validation_messages():
+    B, HV, K, V = 2, 3, 16, 8
+    st = sq.init_quant_state(torch.randn(B, HV, K, V), 8, sq.RES_INT8)
+    q = k = torch.zeros(B, HV, K)
+    v = torch.zeros(B, HV, V)
+    al = be = torch.ones(B, HV)
+    base = dict(q=q, k=k, v=v, alpha=al, beta=be)
+    call = lambda st_=st, **kw: sq.gdn_quant_step_fused(*st_, **{**base, **kw}, res_fmt=sq.RES_INT8)
+    with pytest.raises(ValueError, match="q must be"):
+        call(q=q[:, :2])
+    with pytest.raises(ValueError, match="v must be"):
+        call(v=q)
+    with pytest.raises(ValueError, match="alpha must be"):
+        call(alpha=al[0])
+    with pytest.raises(ValueError, match="scale must be"):
+        call((st[0], st[1][:, :, :4], st[2], st[3]))
+    with pytest.raises(ValueError, match="e must be"):
+        call((st[0], st[1], st[2][:, :, :8], st[3]))
+    with pytest.raises(ValueError, match="k is on meta"):
+        call(k=torch.zeros(B, HV, K, device="meta"))
+    with pytest.raises(ValueError, match="beta must be"):
+        sq.gdn_step_fused_fp32(torch.zeros(B, HV, K, V), q, k, v, al, be[:1])
 
 
 @pytest.mark.parametrize("qmax", [3, 7, 15, 31, 63, 127])

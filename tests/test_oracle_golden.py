@@ -107,6 +107,23 @@ def test_mechanism_arms_match_golden():
         assert rel(g[f"head_ef_{bits}"]) < rel(g[f"head_noef_{bits}"])
 
 
+def test_config1_full_size_mechanism_matches_golden():
+    """BASELINE config 1 at its stated size (T = 2000, 4 heads, 128 x 128): the oracle's chain ends in
+    exactly the states the reference's own code produced, error 6.9e-3 (the reference reports 7.0e-3 for
+    its 8-head run of the same recipe)."""
+    import parity
+    torch.set_num_threads(1)
+    g = load_golden("config1_mechanism")
+    h0, q, k, v, alpha, beta, sums = parity.config1_inputs()
+    assert torch.equal(sums, g["input_sums"]), "the seeded draws differ from the ones the fixture was made with"
+    _, h_ref = orc.gdn_decode(h0, q, k, v, alpha, beta)
+    assert torch.equal(h_ref, g["h_ref"])
+    h_q = orc.chained_ef_decode(h0, q, k, v, alpha, beta, 8, "column", True)
+    assert torch.equal(h_q, g["h_quant"])
+    err = ((h_q - h_ref).norm() / h_ref.norm()).item()
+    assert abs(err - float(g["err"])) < 1e-9 and 6.5e-3 < err < 7.5e-3
+
+
 def test_rounding_ties_match_golden():
     g = load_golden("ties_kv")
     K, V = g["target"].shape
