@@ -17,6 +17,10 @@ from concurrent.futures import ThreadPoolExecutor
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libcarry_gdn.so")
+# Test-only twin of the library, built with CARRY_TEST_WAIT_EXPIRY: one tile's copies never complete and the
+# wait limit is short, so that tests/test_gpu_wait_expiry.py can watch a bounded wait run out.  Nothing
+# in the package loads it.
+WAIT_TEST_LIB = os.path.join(PKG, "libcarry_gdn_waittest.so")
 SOURCES = ("carry_gdn_api.cu", "carry_gdn_generic.cu", "carry_gdn_tile128.cu",
            "carry_gdn_tile128_vk.cu", "carry_gdn_tile128_kv.cu", "carry_gdn_multi.cu",
            "carry_gdn_pool.cu", "carry_gdn_noef128.cu")
@@ -33,9 +37,9 @@ def _nvcc() -> str:
 
 
 def is_stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(WAIT_TEST_LIB):
         return True
-    built = os.path.getmtime(LIB)
+    built = min(os.path.getmtime(LIB), os.path.getmtime(WAIT_TEST_LIB))
     deps = [os.path.join(CSRC, s) for s in SOURCES + HEADERS]
     return any(os.path.getmtime(d) > built for d in deps if os.path.exists(d))
 
@@ -51,24 +55,36 @@ def build(force: bool = False, verbose: bool = False) -> str:
     obj_dir = os.path.join(root, "build", "obj")
     os.makedirs(obj_dir, exist_ok=True)
 
-    def compile_one(src):
-        obj = os.path.join(obj_dir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-c", "-o", obj, src]
+    # the sources whose code differs in the test-only twin (the streaming and multi-token kernels)
+    twin_sources = ("carry_gdn_tile128_vk.cu", "carry_gdn_tile128_kv.cu", "carry_gdn_multi.cu")
+
+    def compile_one(job):
+        src, twin = job
+        obj = os.path.join(obj_dir, src.replace(".cu", ".waittest.o" if twin else ".o"))
+        cmd = [nvcc, *NVCC_FLAGS, *(("-DCARRY_TEST_WAIT_EXPIRY",) if twin else ()), "-c", "-o", obj, src]
         proc = subprocess.run(cmd, cwd=CSRC, capture_output=True, text=True)
         return obj, cmd, proc
 
-    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
-        results = list(pool.map(compile_one, SOURCES))
+    jobs = [(s, False) for s in SOURCES] + [(s, True) for s in twin_sources]
+    with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+        results = list(pool.map(compile_one, jobs))
     log = []
     failed = False
-    for obj, cmd, proc in results:
-        log.append(" ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+    for (src, twin), (obj, cmd, proc) in zip(jobs, results):
+        if not twin:                                  # the resource report of the shipped library only
+            log.append(" ".join(cmd) + "\n" + proc.stdout + proc.stderr)
+        elif proc.returncode != 0:
+            log.append(" ".join(cmd) + "\n" + proc.stdout + proc.stderr)
         failed = failed or proc.returncode != 0
     if not failed:
-        link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", LIB] + [r[0] for r in results]
-        proc = subprocess.run(link, cwd=CSRC, capture_output=True, text=True)
-        log.append(" ".join(link) + "\n" + proc.stdout + proc.stderr)
-        failed = proc.returncode != 0
+        objs = {job: r[0] for job, r in zip(jobs, results)}
+        main_objs = [objs[(s, False)] for s in SOURCES]
+        twin_objs = [objs[(s, s in twin_sources)] for s in SOURCES]
+        for target, members in ((LIB, main_objs), (WAIT_TEST_LIB, twin_objs)):
+            link = [nvcc, "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", target] + members
+            proc = subprocess.run(link, cwd=CSRC, capture_output=True, text=True)
+            log.append(" ".join(link) + "\n" + proc.stdout + proc.stderr)
+            failed = failed or proc.returncode != 0
     text = "\n".join(log)
     with open(os.path.join(root, "build", "ptxas.log"), "w") as f:
         f.write(text)

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
     mbar_init(&full_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     // the state of the tile: codes, residual, state scales, residual scale(s)
-    mbar_arrive_expect_tx(&full_bar, kT * kT + L::kResidBytes + 512 + L::kRScaleBytes);
+    mbar_arrive_expect_tx(&full_bar, kT * kT + L::kResidBytes + 512 + L::kRScaleBytes + test_extra_tx(tile));
     bulk_load(sb + L::kCodes, reinterpret_cast<const void*>(a8[D_CODES]), kT * kT, &full_bar);
     bulk_load(sb + L::kResid, reinterpret_cast<const void*>(a8[D_RESID]), L::kResidBytes, &full_bar);
     bulk_load(sb + L::kSScale, reinterpret_cast<const void*>(a8[D_SSCALE]), 512, &full_bar);
@@ -155,7 +155,10 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
   }
 
   __syncthreads();
-  if (!healthy || *poison) return;                   // the copies never arrived: leave the pool as it was
+  if (!healthy || *poison) {                         // the copies never arrived: leave the pool as it was,
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);  // after a bounded while for whatever is still on its way
+    return;
+  }
   // the tile goes back to the pool: 16 bytes per thread and step, whole lines
   for (int i = tid; i < kT * kT / 16; i += kThreads)
     stg_v4(addr[D_CODES] + 16ull * i, *reinterpret_cast<const uint4*>(sb + L::kCodes + 16 * i));

@@ -45,7 +45,17 @@ namespace {
 constexpr int kT = 128;                 // tile edge
 constexpr int kThreads = 256;          // threads of one group: the 8 warps that share a tile
 constexpr int kWarps = 8;
+// Polls of a stage barrier before a wait gives up.  CARRY_TEST_WAIT_EXPIRY builds a test-only library in
+// which the copies of global tile 1 announce 16 bytes more than they bring, so that its barrier never
+// completes, and the limit is short: the expiry path (status bit, poisoned CTA, pool left untouched) then
+// runs in a fraction of a millisecond without anything faulting or hanging.
+#ifdef CARRY_TEST_WAIT_EXPIRY
+constexpr uint32_t kSpinLimit = 1u << 11;
+__device__ __forceinline__ uint32_t test_extra_tx(int tile) { return tile == 1 ? 16u : 0u; }
+#else
 constexpr uint32_t kSpinLimit = 1u << 22;
+__device__ __forceinline__ uint32_t test_extra_tx(int) { return 0u; }
+#endif
 constexpr int kTileCache = 64;         // per group: cached slot ids and gates of the CTA's first tiles
 
 enum { LAYOUT_VK = 0, LAYOUT_KV = 1 };  // slot layout [V][K]; statequant layout [K][V]
@@ -547,14 +557,15 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
 // bytes were announced cost 20 % of the kernel's time when measured.  `slot` <= 0 marks a padding request:
 // nothing is copied.
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__device__ __forceinline__ void issue_copies(const KParams& p, uint8_t* sb, uint64_t* bar, const unsigned long long (&a)[8]) {
+__device__ __forceinline__ void issue_copies(const KParams& p, uint8_t* sb, uint64_t* bar, const unsigned long long (&a)[8],
+                                             int tile) {
   using L = StageLayout<RES, LAYOUT, QDT, RSCALE>;
   constexpr uint32_t rscale_bytes = L::kRScaleBytes;
   // launch-wide offsets from where results go to where the state is read (zero when in place)
   const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
   const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
   const long long d_sscale = reinterpret_cast<const uint8_t*>(p.sscale_in) - reinterpret_cast<const uint8_t*>(p.sscale_out);
-  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes);
+  mbar_arrive_expect_tx(bar, kT * kT + L::kResidBytes + 512 + rscale_bytes + 3 * L::kVecBytes + test_extra_tx(tile));
   bulk_load(sb + L::kCodes, reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT, bar);
   bulk_load(sb + L::kResid, reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes, bar);
   bulk_load(sb + L::kSScale, reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512, bar);
@@ -569,18 +580,19 @@ __device__ __noinline__ void issue_tile(const KParams& p, uint8_t* sb, uint64_t*
   if (slot <= 0 || (p.packed && slot >= p.num_slots)) { mbar_arrive(bar); return; }
   unsigned long long a[8];
   tile_addresses<RES, RSCALE, QDT>(p, n, hv, h, slot, a);
-  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a);
+  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a, n * p.HV + hv);
 }
 // ... from the addresses worked out when the CTA started
 template <int LAYOUT, int RES, int RSCALE, int QDT>
-__device__ __noinline__ void issue_cached(const KParams& p, uint8_t* sb, uint64_t* bar, const TileDesc* d, int slot) {
+__device__ __noinline__ void issue_cached(const KParams& p, uint8_t* sb, uint64_t* bar, const TileDesc* d, int slot,
+                                          int tile) {
   if (slot <= 0) { mbar_arrive(bar); return; }
   const uint4 w0 = lds_v4(d), w1 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 16);
   const uint4 w2 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 32), w3 = lds_v4(reinterpret_cast<const uint8_t*>(d) + 48);
   auto u64 = [](uint32_t lo, uint32_t hi) { return ((unsigned long long)hi << 32) | lo; };
   const unsigned long long a[8] = {u64(w0.x, w0.y), u64(w0.z, w0.w), u64(w1.x, w1.y), u64(w1.z, w1.w),
                                    u64(w2.x, w2.y), u64(w2.z, w2.w), u64(w3.x, w3.y), u64(w3.z, w3.w)};
-  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a);
+  issue_copies<LAYOUT, RES, RSCALE, QDT>(p, sb, bar, a, tile);
 }
 
 // ---------------------------------------------------------------------------
@@ -664,7 +676,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   auto load_tile = [&](int num) {                   // one thread requests tile `num`
     uint8_t* dst_stage = smem + (size_t)(num % S) * L::kBytes;
     if (num < kCache) {
-      issue_cached<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], &desc_cache[num], meta_cache[num].slot);
+      issue_cached<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], &desc_cache[num], meta_cache[num].slot,
+                                             (int)blockIdx.x + num * (int)gridDim.x);
     } else {
       const int tile = (int)blockIdx.x + num * (int)gridDim.x;
       int tn, thv, th;
@@ -1000,6 +1013,11 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     it = *reinterpret_cast<volatile int*>(&claimed[grp][cnt & 1]);   // written before this tile's last meeting
   }
   __syncthreads();
+  // A CTA whose wait ran out has stopped requesting tiles, but copies it requested earlier may still be on
+  // their way into its shared memory: give them a bounded while to land before the CTA leaves the SM.
+  if (*poison) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
 }
 
 template <int LAYOUT, int RES, int RSCALE, int QDT>

@@ -221,5 +221,3 @@ def test_config1_mechanism_full_size_on_the_gpu():
     rel = lambda x, y: ((x - y).norm() / y.norm()).item()
     err = rel(h_gpu, g["h_ref"])
     assert abs(err - float(g["err"])) < 0.05 * float(g["err"]), f"{err:.4e} vs {float(g['err']):.4e}"
-    # and it tracks the reference's own quantised chain far more closely than either tracks the exact one
-    assert rel(h_gpu, g["h_quant"]) < 0.5 * float(g["err"])
