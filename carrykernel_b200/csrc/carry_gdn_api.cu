@@ -77,6 +77,11 @@ int packed_params(const CarryGdnPackedArgs* a, KParams& p) {
 }
 }  // namespace carry
 
+// The runtime keeps a per-thread "last error" until somebody reads it.  Every entry point reads it away
+// first, so that a launch failure reported by this library is this call's and not a leftover of the host
+// program's earlier CUDA calls (sticky errors, i.e. a lost context, come back on the next call anyway).
+static inline void clear_stale_error() { (void)cudaGetLastError(); }
+
 extern "C" {
 
 int carry_gdn_abi_version(void) { return CARRY_GDN_ABI_VERSION; }
@@ -99,6 +104,7 @@ const char* carry_gdn_strerror(int code) {
 }
 
 int carry_gdn_quant_step(const CarryGdnStepArgs* a, void* stream) {
+  clear_stale_error();
   if (!a) return CARRY_GDN_ERR_NULL;
   if (a->B < 0 || a->HV < 0 || a->K <= 0 || a->V <= 0) return CARRY_GDN_ERR_SHAPE;
   if (!(a->qmax >= 1.0f && a->qmax <= 127.0f)) return CARRY_GDN_ERR_SHAPE;
@@ -135,6 +141,7 @@ int carry_gdn_quant_step(const CarryGdnStepArgs* a, void* stream) {
 }
 
 int carry_gdn_fp32_step(const CarryGdnFp32Args* a, void* stream) {
+  clear_stale_error();
   if (!a) return CARRY_GDN_ERR_NULL;
   if (a->B < 0 || a->HV < 0 || a->K <= 0 || a->V <= 0) return CARRY_GDN_ERR_SHAPE;
   if (!dtype_ok(a->qkv_dtype) || !dtype_ok(a->o_dtype)) return CARRY_GDN_ERR_DTYPE;
@@ -147,6 +154,7 @@ int carry_gdn_fp32_step(const CarryGdnFp32Args* a, void* stream) {
 }
 
 int carry_gdn_packed_decode(const CarryGdnPackedArgs* a, void* stream) {
+  clear_stale_error();
   carry::KParams p;
   const int rc = carry::packed_params(a, p);
   if (rc != CARRY_GDN_OK || a->B == 0) return rc;
@@ -154,6 +162,7 @@ int carry_gdn_packed_decode(const CarryGdnPackedArgs* a, void* stream) {
 }
 
 int carry_gdn_packed_decode_multi(const CarryGdnPackedMultiArgs* m, void* stream) {
+  clear_stale_error();
   if (!m) return CARRY_GDN_ERR_NULL;
   if (m->T < 1) return CARRY_GDN_ERR_SHAPE;
   carry::KParams p;
@@ -181,6 +190,7 @@ bool pool_has_pointers(const CarryGdnPool& pool) {
 }  // namespace
 
 int carry_gdn_pool_store(const CarryGdnPoolStoreArgs* a, void* stream) {
+  clear_stale_error();
   if (!a) return CARRY_GDN_ERR_NULL;
   if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
   const int rc = pool_ok(a->pool);
@@ -195,6 +205,7 @@ int carry_gdn_pool_store(const CarryGdnPoolStoreArgs* a, void* stream) {
 }
 
 int carry_gdn_pool_load(const CarryGdnPoolLoadArgs* a, void* stream) {
+  clear_stale_error();
   if (!a) return CARRY_GDN_ERR_NULL;
   if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
   const int rc = pool_ok(a->pool);
@@ -208,6 +219,7 @@ int carry_gdn_pool_load(const CarryGdnPoolLoadArgs* a, void* stream) {
 }
 
 int carry_gdn_pool_copy(const CarryGdnPoolCopyArgs* a, void* stream) {
+  clear_stale_error();
   if (!a) return CARRY_GDN_ERR_NULL;
   if (a->B < 0) return CARRY_GDN_ERR_SHAPE;
   int rc = pool_ok(a->src);

@@ -316,8 +316,8 @@ int launch_generic(const KParams& p, cudaStream_t stream) {
   if (smem > kMaxSmem) return CARRY_GDN_ERR_UNSUPPORTED;
   static thread_local size_t configured[64] = {0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return CARRY_GDN_ERR_NO_DEVICE;
-  if (dev < 64 && smem > configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return CARRY_GDN_ERR_NO_DEVICE;
+  if (smem > configured[dev]) {
     if (cudaFuncSetAttribute(gdn_generic_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kMaxSmem) != cudaSuccess) {
       cudaGetLastError();
@@ -345,8 +345,8 @@ int launch_fp32(const CarryGdnFp32Args& a, cudaStream_t stream) {
   if (smem > kMaxSmem) return CARRY_GDN_ERR_UNSUPPORTED;
   static thread_local size_t configured[64] = {0};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return CARRY_GDN_ERR_NO_DEVICE;
-  if (dev < 64 && smem > configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return CARRY_GDN_ERR_NO_DEVICE;
+  if (smem > configured[dev]) {
     if (cudaFuncSetAttribute(gdn_fp32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)kMaxSmem) != cudaSuccess) {
       cudaGetLastError();

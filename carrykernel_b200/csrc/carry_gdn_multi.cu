@@ -180,8 +180,8 @@ int launch_multi_variant(const KParams& p, const MultiExtra& x, cudaStream_t str
   const size_t smem = (size_t)L::kBytes;
   static thread_local bool configured[64] = {false};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return CARRY_GDN_ERR_NO_DEVICE;
-  if (dev < 64 && !configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return CARRY_GDN_ERR_NO_DEVICE;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
       return CARRY_GDN_ERR_NO_DEVICE;

@@ -1027,8 +1027,8 @@ int launch_variant(const KParams& p, cudaStream_t stream, int sms) {
   const size_t smem = (size_t)L::kBytes * L::kStages;
   static thread_local bool configured[64] = {false};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return CARRY_GDN_ERR_NO_DEVICE;
-  if (dev < 64 && !configured[dev]) {
+  if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64) return CARRY_GDN_ERR_NO_DEVICE;
+  if (!configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
       return CARRY_GDN_ERR_NO_DEVICE;

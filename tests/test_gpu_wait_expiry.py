@@ -1,0 +1,158 @@
+"""A bounded wait that runs out, on the GPU, without faulting or hanging anything.
+
+Every wait of the streaming kernels on data in flight gives up after a fixed
+number of polls, sets ``STATUS_TIMEOUT`` in the status word, and the CTA stops
+loading and storing.  ``libcarry_gdn_waittest.so`` is the same library built with
+``CARRY_TEST_WAIT_EXPIRY``: the copies of global tile 1 (request 0, head 1)
+announce 16 bytes more than they bring, so that tile's stage barrier can never
+complete, and the poll limit is short.  Expected of every kernel: the launch
+returns, the status bit is set, the tile's state and output are exactly as they
+were, and every other tile equals what the regular library computes.
+"""
+
+from __future__ import annotations
+
+import contextlib
+
+import pytest
+import torch
+
+from oracle import gdn_oracle as orc
+from parity import make_packed_inputs, seeded_inputs
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@contextlib.contextmanager
+def wait_test_library():
+    """Route the package's calls through the test-only twin for the duration of the block."""
+    from carrykernel_b200 import _build, _lib
+    saved = _lib._lib
+    _lib._lib = None
+    try:
+        _lib.load_library(_build.WAIT_TEST_LIB)
+        yield
+    finally:
+        _lib._lib = saved
+
+
+def _slot_case(resid_fmt, rscale):
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    B, H, HV, K, V, num_slots = 4, 32, 32, 128, 128, 6
+    g = torch.Generator().manual_seed(3)
+    pool = torch.randn(num_slots, HV, V, K, generator=g) * 0.1
+    st = [x.to(DEV) for x in qpd.init_quantized_state(num_slots, HV, V, K, "cpu", h0=pool, resid_fmt=resid_fmt,
+                                                      resid_scale=rscale)]
+    idx = torch.tensor([3, 1, 5, 2], dtype=torch.int32, device=DEV)
+    return qpd, (B, H, HV, K, V), st, idx
+
+
+@pytest.mark.parametrize("resid_fmt,rscale", [(1, "head"), (0, "v")])
+def test_single_token_kernel_wait_runs_out(resid_fmt, rscale):
+    from carrykernel_b200 import _lib
+    qpd, (B, H, HV, K, V), st, idx = _slot_case(resid_fmt, rscale)
+    mixed, a, b, A_log, dt_bias = [x.to(DEV) for x in make_packed_inputs(B, H, HV, K, V, seed=9, dtype=torch.bfloat16)]
+    A_log, dt_bias = A_log.float(), dt_bias.float()
+
+    def run(pool, status):
+        out = torch.full((B, 1, HV, V), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, K ** -0.5, *pool, out, idx,
+                                                     use_qk_l2norm_in_kernel=True, resid_fmt=resid_fmt, status=status)
+        torch.cuda.synchronize()
+        return out
+
+    good = [x.clone() for x in st]
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out_good = run(good, status)
+    assert int(status.item()) == 0
+    bad = [x.clone() for x in st]
+    with wait_test_library():
+        out_bad = run(bad, status)
+    assert int(status.item()) == _lib.STATUS_TIMEOUT
+    slot, head = int(idx[0]), 1                      # global tile 1 = request 0, head 1
+    # that tile: nothing written
+    assert torch.isnan(out_bad[0, 0, head].float()).all()
+    for x_bad, x0 in zip(bad[:3], st[:3]):
+        assert torch.equal(x_bad[slot, head], x0[slot, head])
+    assert torch.equal(bad[3][slot, head], st[3][slot, head])
+    # every other tile: what the regular library computes
+    keep = torch.ones(B, HV, dtype=torch.bool, device=DEV)
+    keep[0, head] = False
+    assert torch.equal(out_bad[:, 0][keep], out_good[:, 0][keep])
+    mask = torch.ones(st[0].shape[0], HV, dtype=torch.bool, device=DEV)
+    mask[slot, head] = False
+    for x_bad, x_good in zip(bad, good):
+        assert torch.equal(x_bad[mask], x_good[mask])
+    # the context is still usable and the regular library still clean
+    status.zero_()
+    run([x.clone() for x in st], status)
+    assert int(status.item()) == 0
+
+
+def test_multi_token_kernel_wait_runs_out():
+    from carrykernel_b200 import _lib
+    qpd, (B, H, HV, K, V), st, idx = _slot_case(1, "head")
+    T = 2
+    toks = [make_packed_inputs(B, H, HV, K, V, seed=20 + t, dtype=torch.bfloat16) for t in range(T)]
+    mixed = torch.stack([x[0] for x in toks], 1).to(DEV)
+    a = torch.stack([x[1] for x in toks], 1).to(DEV)
+    b = torch.stack([x[2] for x in toks], 1).to(DEV)
+    A_log, dt_bias = toks[0][3].to(DEV), toks[0][4].to(DEV)
+
+    def run(pool, status):
+        out = torch.full((B, T, HV, V), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qpd.quantized_gated_delta_rule_packed_decode_multi(mixed, a, b, A_log, dt_bias, K ** -0.5, *pool, out, idx,
+                                                           use_qk_l2norm_in_kernel=True, resid_fmt=1, status=status)
+        torch.cuda.synchronize()
+        return out
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    good = [x.clone() for x in st]
+    out_good = run(good, status)
+    assert int(status.item()) == 0
+    bad = [x.clone() for x in st]
+    with wait_test_library():
+        out_bad = run(bad, status)
+    assert int(status.item()) == _lib.STATUS_TIMEOUT
+    slot, head = int(idx[0]), 1
+    assert torch.isnan(out_bad[0, :, head].float()).all()
+    for x_bad, x0 in zip(bad, st):
+        assert torch.equal(x_bad[slot, head], x0[slot, head])
+    keep = torch.ones(B, HV, dtype=torch.bool, device=DEV)
+    keep[0, head] = False
+    assert torch.equal(out_bad.transpose(1, 2)[keep], out_good.transpose(1, 2)[keep])
+    mask = torch.ones(st[0].shape[0], HV, dtype=torch.bool, device=DEV)
+    mask[slot, head] = False
+    for x_bad, x_good in zip(bad, good):
+        assert torch.equal(x_bad[mask], x_good[mask])
+
+
+def test_statequant_layout_kernel_wait_runs_out():
+    from carrykernel_b200 import _lib
+    from carrykernel_b200.statequant import kernel as sq
+    B, HV, K, V = 3, 8, 128, 128
+    h0, q, k, v, alpha, beta = seeded_inputs(B, HV, K, V, seed=4, alpha_mode="gated")
+    st = [x.to(DEV) for x in orc.init_quant_state(h0, 8, orc.RES_INT8)]
+    acts = [x.to(DEV) for x in (q, k, v, alpha, beta)]
+
+    def run(status):
+        outs = (torch.full((B, HV, V), float("nan"), device=DEV), torch.full_like(st[0], 77),
+                torch.full_like(st[1], -1.0), torch.full_like(st[2], 77), torch.full_like(st[3], -1.0))
+        sq.quant_step_into(*st, *acts, outs, 8, orc.RES_INT8, "v", "v", status=status)
+        torch.cuda.synchronize()
+        return outs
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    good = run(status)
+    assert int(status.item()) == 0
+    with wait_test_library():
+        bad = run(status)
+    assert int(status.item()) == _lib.STATUS_TIMEOUT
+    n, head = 0, 1
+    assert torch.isnan(bad[0][n, head]).all()
+    assert torch.all(bad[1][n, head] == 77) and torch.all(bad[2][n, head] == -1) and torch.all(bad[3][n, head] == 77)
+    keep = torch.ones(B, HV, dtype=torch.bool, device=DEV)
+    keep[n, head] = False
+    for x_bad, x_good in zip(bad, good):
+        assert torch.equal(x_bad[keep], x_good[keep])
