@@ -156,6 +156,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
 
   __syncthreads();
   if (!healthy || *poison) {                         // the copies never arrived: leave the pool as it was,
+#pragma unroll 1
     for (int i = 0; i < 200; ++i) __nanosleep(1000);  // after a bounded while for whatever is still on its way
     return;
   }

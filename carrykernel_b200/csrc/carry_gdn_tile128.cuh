@@ -1016,6 +1016,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   // A CTA whose wait ran out has stopped requesting tiles, but copies it requested earlier may still be on
   // their way into its shared memory: give them a bounded while to land before the CTA leaves the SM.
   if (*poison) {
+#pragma unroll 1
     for (int i = 0; i < 200; ++i) __nanosleep(1000);
   }
 }
