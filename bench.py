@@ -68,6 +68,7 @@ assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
 # of the results is inside the window), keyed by the SHA-256 of the kernel sources the profiled library
 # was built from.  A library built from other sources gets null until it has been profiled again.
 NCU_TRAFFIC_BY_SOURCE = {
+    "0e61b8339dd81fb5": 103_790_000,
 }
 KERNEL_SOURCES = ("carry_gdn_tile128.cuh", "carry_gdn_slot_tile.inc", "carry_gdn_common.cuh")
 
@@ -748,8 +749,8 @@ def headtohead(batches=(1, 8, 16, 64, 256), steps=200, warmup=50, seed=0):
         if vllm_fn is not None:
             st = qpd.init_quantized_state(B + 1, HHV, V, K, dev, h0=h0, resid_fmt=qpd.RESID_INT4, resid_scale="head")
             h_deq = st[0].float() * st[1][..., None]
-            o_v = torch.empty(B, 1, HHV, V, device=dev)
-            o_o = torch.empty(B, 1, HHV, V, device=dev)
+            o_v = torch.full((B, 1, HHV, V), float("nan"), device=dev)
+            o_o = torch.full((B, 1, HHV, V), float("nan"), device=dev)
             vllm_fn(mixed_qkv=mixed, a=a, b=b, A_log=A_log, dt_bias=dt_bias, scale=scale, initial_state=h_deq,
                     out=o_v, ssm_state_indices=idx, use_qk_l2norm_in_kernel=True)
             qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, scale, *st, o_o, idx,
@@ -757,6 +758,7 @@ def headtohead(batches=(1, 8, 16, 64, 256), steps=200, warmup=50, seed=0):
             torch.cuda.synchronize()
             row["out_max_abs_diff_vs_vllm_fp32"] = float((o_o - o_v).abs().max())
             row["out_max_rel_diff_vs_vllm_fp32"] = float(((o_o - o_v).abs() / (o_v.abs() + 1e-4)).max())
+            row["out_mean_abs"] = {"vllm": float(o_v.abs().mean()), "ours": float(o_o.abs().mean())}
         elems = B * HHV * V * K
         row["state_traffic_MB"] = {
             "vllm_fp32": 2 * elems * 4 / 1e6, "vllm_bf16": 2 * elems * 2 / 1e6,

@@ -24,6 +24,7 @@ def test_headtohead_guard_and_numeric_agreement():
     for key in ("ours_int8_resid_v_us", "ours_int8_resid_head_us", "ours_int4_resid_v_us", "ours_int4_resid_head_us"):
         assert row[key] > 0
     # same state, same fp32 inputs: the two kernels differ only in summation order
+    assert row["out_mean_abs"]["vllm"] > 1e-3 and row["out_mean_abs"]["ours"] > 1e-3, row     # not vacuous
     assert row["out_max_abs_diff_vs_vllm_fp32"] < 1e-4, row
     assert row["out_max_rel_diff_vs_vllm_fp32"] < 1e-3, row
     assert row["state_traffic_MB"]["ours_int4_resid"] < row["state_traffic_MB"]["vllm_bf16"]
