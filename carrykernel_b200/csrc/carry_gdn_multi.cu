@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
         *reinterpret_cast<uint4*>(&vec_t[tt][16 * c]) = __ldg(reinterpret_cast<const uint4*>(src) + cc);
       }
       if (warp < nt)
-        tile_meta4<RES, RSCALE, QDT>(p, tile, lane & 3, lane < 4, &meta_t[warp], nullptr,
+        tile_meta<RES, RSCALE, QDT, 32>(p, tile, lane, true, &meta_t[warp], nullptr,
                                      (long long)(t + warp) * x.stride_mixed_t, (long long)(t + warp) * x.stride_a_t,
                                      (long long)(t + warp) * x.stride_b_t);
       __syncthreads();

@@ -476,19 +476,26 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
   }
 }
 
-// Computed by four consecutive lanes straight from global memory: slot id, gates, and the norms of k
-// and q (32 elements per lane, then a sum over the four lanes).  Every load depends on the tile index
-// alone, so the whole thing is one trip to memory however many tiles a CTA prepares at once.  All 32
-// lanes of a warp must call this together; when `store` is set the first lane of a group writes `dst`
-// and each of the four lanes a quarter of the tile's addresses to `ddst`.  A slot id beyond the pool is
-// reported in the status word and treated as padding.
+// Computed by LPT consecutive lanes (4, 8 or 32) straight from global memory: slot id, gates, and the
+// norms of k and q (128 / LPT elements per lane, then a sum over the LPT lanes).  Every load depends on the
+// tile index alone, so the whole thing is one trip to memory however many tiles a CTA prepares at once.  The
+// more lanes share a tile the shorter each lane's instruction stream: a CTA with few tiles (a small batch)
+// gives a whole warp to each, and its first tile can start that much sooner.  The sums are always taken
+// in the same order -- groups of four consecutive elements, then a balanced tree over the groups in index
+// order -- so the result does not depend on LPT (nor on which kernel of this library asks).
+// All 32 lanes of a warp must call this together; when `store` is set, lane 0 of a tile's lanes writes `dst`
+// and lanes 0..3 a quarter of the tile's addresses each to `ddst`.  A slot id beyond the pool is reported in
+// the status word and treated as padding.
 // (tok_*: element offsets of the token within its request, for callers that take several tokens per
 // request; `ddst` may be null.)
-template <int RES, int RSCALE, int QDT>
-__device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst,
-                                        long long tok_qkv = 0, long long tok_a = 0, long long tok_b = 0) {
+template <int RES, int RSCALE, int QDT, int LPT>
+__device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst,
+                                       long long tok_qkv = 0, long long tok_a = 0, long long tok_b = 0) {
+  static_assert(LPT == 4 || LPT == 8 || LPT == 32, "lanes per tile");
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
-  constexpr int kVecs = 32 * qes / 16;                 // 16-byte loads per lane and vector
+  constexpr int E = kT / LPT;                          // elements per lane and vector
+  constexpr int kWords = E * qes / 4;                  // 32-bit words per lane and vector
+  constexpr int kGroups4 = E / 4;                      // groups of four elements per lane
   TileMeta m;
   int hv, h;
   split_tile(p, tile, m.n, hv, h);
@@ -500,50 +507,68 @@ __device__ __noinline__ void tile_meta4(const KParams& p, int tile, int sub, boo
   } else {
     q_off = k_off = ((long long)m.n * p.HV + hv) * kT;
   }
-  const uint4* qp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.q) + (q_off + 32 * sub) * qes);
-  const uint4* kp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(p.k) + (k_off + 32 * sub) * qes);
-  uint4 qv[kVecs], kv[kVecs];
+  const uint8_t* qp = reinterpret_cast<const uint8_t*>(p.q) + (q_off + E * sub) * qes;
+  const uint8_t* kp = reinterpret_cast<const uint8_t*>(p.k) + (k_off + E * sub) * qes;
+  uint32_t qw[kWords], kw[kWords];
+  if constexpr (kWords >= 4) {
 #pragma unroll
-  for (int j = 0; j < kVecs; ++j) { qv[j] = __ldg(qp + j); kv[j] = __ldg(kp + j); }
+    for (int j = 0; j < kWords / 4; ++j) {
+      const uint4 a = __ldg(reinterpret_cast<const uint4*>(qp) + j), b = __ldg(reinterpret_cast<const uint4*>(kp) + j);
+      qw[4 * j] = a.x; qw[4 * j + 1] = a.y; qw[4 * j + 2] = a.z; qw[4 * j + 3] = a.w;
+      kw[4 * j] = b.x; kw[4 * j + 1] = b.y; kw[4 * j + 2] = b.z; kw[4 * j + 3] = b.w;
+    }
+  } else {
+    static_assert(kWords == 2, "a lane's share of a vector is at least 8 bytes");
+    const uint2 a = __ldg(reinterpret_cast<const uint2*>(qp)), b = __ldg(reinterpret_cast<const uint2*>(kp));
+    qw[0] = a.x; qw[1] = a.y; kw[0] = b.x; kw[1] = b.y;
+  }
   m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
   gates_of(p, m.n, hv, m.alpha, m.beta, tok_a, tok_b);
-  float ks = 0.f, qs = 0.f, kq = 0.f;
+  float ks[kGroups4], qs[kGroups4], kq[kGroups4];
 #pragma unroll
-  for (int j = 0; j < kVecs; ++j) {
-    const uint32_t qw[4] = {qv[j].x, qv[j].y, qv[j].z, qv[j].w}, kw[4] = {kv[j].x, kv[j].y, kv[j].z, kv[j].w};
+  for (int g = 0; g < kGroups4; ++g) {                 // four consecutive elements: one chain each
+    float a[4], b[4];
+    if (QDT == CARRY_F32) {
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      if (QDT == CARRY_F32) {
-        const float a = __uint_as_float(kw[c]), b = __uint_as_float(qw[c]);
-        ks = fmaf(a, a, ks); qs = fmaf(b, b, qs); kq = fmaf(a, b, kq);
-      } else {
-        const float2 a = act_pair<QDT>(kw[c]), b = act_pair<QDT>(qw[c]);
-        ks = fmaf(a.x, a.x, ks); qs = fmaf(b.x, b.x, qs); kq = fmaf(a.x, b.x, kq);
-        ks = fmaf(a.y, a.y, ks); qs = fmaf(b.y, b.y, qs); kq = fmaf(a.y, b.y, kq);
+      for (int c = 0; c < 4; ++c) { a[c] = __uint_as_float(kw[4 * g + c]); b[c] = __uint_as_float(qw[4 * g + c]); }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const float2 ka = act_pair<QDT>(kw[2 * g + c]), qa = act_pair<QDT>(qw[2 * g + c]);
+        a[2 * c] = ka.x; a[2 * c + 1] = ka.y; b[2 * c] = qa.x; b[2 * c + 1] = qa.y;
       }
     }
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) { s0 = fmaf(a[c], a[c], s0); s1 = fmaf(b[c], b[c], s1); s2 = fmaf(a[c], b[c], s2); }
+    ks[g] = s0; qs[g] = s1; kq[g] = s2;
   }
 #pragma unroll
-  for (int o = 1; o <= 2; o <<= 1) {
-    ks += __shfl_xor_sync(0xffffffffu, ks, o);
-    qs += __shfl_xor_sync(0xffffffffu, qs, o);
-    kq += __shfl_xor_sync(0xffffffffu, kq, o);
+  for (int stride = 1; stride < kGroups4; stride *= 2)   // balanced tree over this lane's groups, in index order
+#pragma unroll
+    for (int g = 0; g + stride < kGroups4; g += 2 * stride) { ks[g] += ks[g + stride]; qs[g] += qs[g + stride]; kq[g] += kq[g + stride]; }
+  float ksum = ks[0], qsum = qs[0], kqsum = kq[0];
+#pragma unroll
+  for (int o = 1; o < LPT; o <<= 1) {                    // ... and on over the tile's lanes
+    ksum += __shfl_xor_sync(0xffffffffu, ksum, o);
+    qsum += __shfl_xor_sync(0xffffffffu, qsum, o);
+    kqsum += __shfl_xor_sync(0xffffffffu, kqsum, o);
   }
   m.k_mul = 1.0f; m.q_mul = 1.0f;
   if (p.packed) {
     if (p.l2norm) {
-      m.k_mul = __frcp_rn(sqrtf(ks + 1e-6f));
-      m.q_mul = __frcp_rn(sqrtf(qs + 1e-6f));
+      m.k_mul = __frcp_rn(sqrtf(ksum + 1e-6f));
+      m.q_mul = __frcp_rn(sqrtf(qsum + 1e-6f));
     }
     m.q_mul *= p.qscale;
   }
-  m.kq = kq * (m.k_mul * m.q_mul);
+  m.kq = kqsum * (m.k_mul * m.q_mul);
   if (p.packed && m.slot >= p.num_slots) {
     if (store && sub == 0 && p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
     m.slot = 0;
   }
   if (store && sub == 0) *dst = m;
-  if (store && ddst) {
+  if (store && ddst && sub < 4) {
     unsigned long long a[8];
     tile_addresses<RES, RSCALE, QDT>(p, m.n, hv, h, m.slot > 0 ? m.slot : 0, a);
     const unsigned long long lo = (sub == 0) ? a[0] : (sub == 1) ? a[2] : (sub == 2) ? a[4] : a[6];
@@ -661,12 +686,26 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   }
   __syncwarp();
   {
-    static_assert(kThreads / 4 == kTileCache, "four lanes prepare one tile");
-    const int i = tid >> 2;
-    const bool valid = i < my_tiles;
-    if (warp * 8 < my_tiles)                         // warps without a tile to prepare stay out of the way
-      tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
-                                   &meta_cache[i], &desc_cache[i]);
+    // lanes per tile: as many as the CTA's tile count leaves room for in one pass over its threads
+    static_assert(kThreads / 4 == kTileCache, "at four lanes per tile one pass covers the whole cache");
+    const int cached = my_tiles < kCache ? my_tiles : kCache;
+    if (cached <= G * kWarps) {                      // a warp per tile
+      if (warp < cached)
+        tile_meta<RES, RSCALE, QDT, 32>(p, (int)blockIdx.x + warp * (int)gridDim.x, lane, true, &meta_cache[warp],
+                                        &desc_cache[warp]);
+    } else if (cached <= G * kWarps * 4) {           // eight lanes per tile
+      const int i = tid >> 3;
+      const bool valid = i < cached;
+      if (warp * 4 < cached)
+        tile_meta<RES, RSCALE, QDT, 8>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 7, valid,
+                                       &meta_cache[i], &desc_cache[i]);
+    } else {                                         // four lanes per tile
+      const int i = tid >> 2;
+      const bool valid = i < cached;
+      if (warp * 8 < cached)                         // warps without a tile to prepare stay out of the way
+        tile_meta<RES, RSCALE, QDT, 4>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
+                                       &meta_cache[i], &desc_cache[i]);
+    }
   }
   __syncthreads();
   static_assert(S <= G * kWarps && S <= kTileCache, "one warp per stage issues the first requests, from the cache");
@@ -712,8 +751,8 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     const int entry = it < kCache ? it : kCache + warp;
     const TileMeta* tm = &meta_cache[entry];
     if (it >= kCache) {
-      tile_meta4<RES, RSCALE, QDT>(p, (int)blockIdx.x + it * (int)gridDim.x, lane & 3, lane < 4, &meta_cache[entry],
-                                   &desc_cache[entry]);
+      tile_meta<RES, RSCALE, QDT, 32>(p, (int)blockIdx.x + it * (int)gridDim.x, lane, true, &meta_cache[entry],
+                                      &desc_cache[entry]);
       __syncwarp();
     }
     const uint4 tm0 = lds_v4(tm);
