@@ -406,17 +406,43 @@ __device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float 
   }
 }
 
-// gates of one (request, head): derived in the kernel on the slot path, given on the other
-__device__ __forceinline__ void gates_of(const KParams& p, int n, int hv, float& alpha, float& beta,
-                                         long long tok_a = 0, long long tok_b = 0) {
+// One scalar of element type `dtype` as raw bits, and the bits as a float.  Split in two so that a caller
+// can have all its loads in flight before the first conversion waits for one: load_as_float() in a row
+// makes every load wait for the previous one's conversion (a trip to memory each).
+__device__ __forceinline__ uint32_t load_raw(const void* p, long long i, int dtype) {
+  if (dtype == CARRY_F32) return __ldg(reinterpret_cast<const uint32_t*>(p) + i);
+  return __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+}
+__device__ __forceinline__ float raw_to_float(uint32_t r, int dtype) {
+  if (dtype == CARRY_F32) return __uint_as_float(r);
+  if (dtype == CARRY_BF16) return __uint_as_float(r << 16);
+  return __half2float(__ushort_as_half((unsigned short)r));
+}
+
+// Gates of one (request, head): derived in the kernel on the slot path, given on the other.  The loads
+// (gate_loads) and the arithmetic (gates_from) are separate calls for the reason above.
+struct GateRaw { uint32_t a, b, A_log, dt_bias; };
+__device__ __forceinline__ GateRaw gate_loads(const KParams& p, int n, int hv, long long tok_a, long long tok_b) {
+  GateRaw r;
   if (p.packed) {
-    slot_gates(load_as_float(p.a, (long long)n * p.stride_a_tok + hv + tok_a, p.ab_dtype),
-               load_as_float(p.b, (long long)n * p.stride_b_tok + hv + tok_b, p.ab_dtype),
-               load_as_float(p.A_log, hv, p.A_log_dtype), load_as_float(p.dt_bias, hv, p.dt_bias_dtype),
-               alpha, beta);
+    r.a = load_raw(p.a, (long long)n * p.stride_a_tok + hv + tok_a, p.ab_dtype);
+    r.b = load_raw(p.b, (long long)n * p.stride_b_tok + hv + tok_b, p.ab_dtype);
+    r.A_log = load_raw(p.A_log, hv, p.A_log_dtype);
+    r.dt_bias = load_raw(p.dt_bias, hv, p.dt_bias_dtype);
   } else {
-    alpha = p.alpha[(long long)n * p.HV + hv];
-    beta = p.beta[(long long)n * p.HV + hv];
+    r.a = __float_as_uint(p.alpha[(long long)n * p.HV + hv]);
+    r.b = __float_as_uint(p.beta[(long long)n * p.HV + hv]);
+    r.A_log = r.dt_bias = 0u;
+  }
+  return r;
+}
+__device__ __forceinline__ void gates_from(const KParams& p, const GateRaw& r, float& alpha, float& beta) {
+  if (p.packed) {
+    slot_gates(raw_to_float(r.a, p.ab_dtype), raw_to_float(r.b, p.ab_dtype), raw_to_float(r.A_log, p.A_log_dtype),
+               raw_to_float(r.dt_bias, p.dt_bias_dtype), alpha, beta);
+  } else {
+    alpha = __uint_as_float(r.a);
+    beta = __uint_as_float(r.b);
   }
 }
 
@@ -523,7 +549,8 @@ __device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool
     qw[0] = a.x; qw[1] = a.y; kw[0] = b.x; kw[1] = b.y;
   }
   m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
-  gates_of(p, m.n, hv, m.alpha, m.beta, tok_a, tok_b);
+  const GateRaw graw = gate_loads(p, m.n, hv, tok_a, tok_b);      // every load of this routine is in flight now
+  gates_from(p, graw, m.alpha, m.beta);
   float ks[kGroups4], qs[kGroups4], kq[kGroups4];
 #pragma unroll
   for (int g = 0; g < kGroups4; ++g) {                 // four consecutive elements: one chain each
