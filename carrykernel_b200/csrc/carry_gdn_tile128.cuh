@@ -96,6 +96,14 @@ __device__ __forceinline__ void bulk_load(void* dst_smem, const void* src_gmem, 
                : "memory");
 }
 
+// Hints to the L2 (no data is consumed, nothing waits): a whole run of bytes, or the lines of a short vector.
+__device__ __forceinline__ void l2_prefetch_bulk(const void* src_gmem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src_gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void l2_prefetch_line(const void* src_gmem) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(src_gmem));
+}
+
 // Bounded wait: after kSpinLimit failed polls the CTA is marked poisoned, the
 // status word gets the timeout bit and every later wait returns at once; a
 // poisoned CTA stops loading and storing.
@@ -410,8 +418,8 @@ __device__ __forceinline__ void redecide_rec(float& e, float& y, float s, float 
 // can have all its loads in flight before the first conversion waits for one: load_as_float() in a row
 // makes every load wait for the previous one's conversion (a trip to memory each).
 __device__ __forceinline__ uint32_t load_raw(const void* p, long long i, int dtype) {
-  if (dtype == CARRY_F32) return __ldg(reinterpret_cast<const uint32_t*>(p) + i);
-  return __ldg(reinterpret_cast<const unsigned short*>(p) + i);
+  if (dtype == CARRY_F32) return __ldcg(reinterpret_cast<const uint32_t*>(p) + i);
+  return __ldcg(reinterpret_cast<const unsigned short*>(p) + i);
 }
 __device__ __forceinline__ float raw_to_float(uint32_t r, int dtype) {
   if (dtype == CARRY_F32) return __uint_as_float(r);
@@ -430,8 +438,8 @@ __device__ __forceinline__ GateRaw gate_loads(const KParams& p, int n, int hv, l
     r.A_log = load_raw(p.A_log, hv, p.A_log_dtype);
     r.dt_bias = load_raw(p.dt_bias, hv, p.dt_bias_dtype);
   } else {
-    r.a = __float_as_uint(p.alpha[(long long)n * p.HV + hv]);
-    r.b = __float_as_uint(p.beta[(long long)n * p.HV + hv]);
+    r.a = __float_as_uint(__ldcg(p.alpha + (long long)n * p.HV + hv));
+    r.b = __float_as_uint(__ldcg(p.beta + (long long)n * p.HV + hv));
     r.A_log = r.dt_bias = 0u;
   }
   return r;
@@ -509,6 +517,9 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
 // gives a whole warp to each, and its first tile can start that much sooner.  The sums are always taken
 // in the same order -- groups of four consecutive elements, then a balanced tree over the groups in index
 // order -- so the result does not depend on LPT (nor on which kernel of this library asks).
+// Every load goes past the L1 (ld.global.cg), which makes the routine safe to run before the kernel's
+// dependency wait with `store` false -- a rehearsal whose results are thrown away: it pulls the
+// routine's instructions and the inputs' lines into the L2, where the real pass then finds them.
 // All 32 lanes of a warp must call this together; when `store` is set, lane 0 of a tile's lanes writes `dst`
 // and lanes 0..3 a quarter of the tile's addresses each to `ddst`.  A slot id beyond the pool is reported in
 // the status word and treated as padding.
@@ -539,16 +550,16 @@ __device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool
   if constexpr (kWords >= 4) {
 #pragma unroll
     for (int j = 0; j < kWords / 4; ++j) {
-      const uint4 a = __ldg(reinterpret_cast<const uint4*>(qp) + j), b = __ldg(reinterpret_cast<const uint4*>(kp) + j);
+      const uint4 a = __ldcg(reinterpret_cast<const uint4*>(qp) + j), b = __ldcg(reinterpret_cast<const uint4*>(kp) + j);
       qw[4 * j] = a.x; qw[4 * j + 1] = a.y; qw[4 * j + 2] = a.z; qw[4 * j + 3] = a.w;
       kw[4 * j] = b.x; kw[4 * j + 1] = b.y; kw[4 * j + 2] = b.z; kw[4 * j + 3] = b.w;
     }
   } else {
     static_assert(kWords == 2, "a lane's share of a vector is at least 8 bytes");
-    const uint2 a = __ldg(reinterpret_cast<const uint2*>(qp)), b = __ldg(reinterpret_cast<const uint2*>(kp));
+    const uint2 a = __ldcg(reinterpret_cast<const uint2*>(qp)), b = __ldcg(reinterpret_cast<const uint2*>(kp));
     qw[0] = a.x; qw[1] = a.y; kw[0] = b.x; kw[1] = b.y;
   }
-  m.slot = p.packed ? p.slot_idx[(long long)m.n * p.stride_idx] : 1;
+  m.slot = p.packed ? __ldcg(p.slot_idx + (long long)m.n * p.stride_idx) : 1;
   const GateRaw graw = gate_loads(p, m.n, hv, tok_a, tok_b);      // every load of this routine is in flight now
   gates_from(p, graw, m.alpha, m.beta);
   float ks[kGroups4], qs[kGroups4], kq[kGroups4];
@@ -692,8 +703,50 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // nothing before this line reads or writes global memory; everything after it sees the results of the
-  // kernels that precede this one in the stream
+  // While the kernel before this one in the stream finishes, ask the L2 for what this CTA reads first: the
+  // state of its groups' first tiles and the activation rows, gate inputs and slot ids of its first tiles
+  // (one lane per tile).  These are hints only -- nothing is consumed here, and the L2 is where that
+  // kernel's writes land, so whatever it still writes is what the loads below will see.  The slot id that
+  // says where a tile's state lives is read past the L1 for the same reason (it only steers the hints: a
+  // stale or wild one costs a useless prefetch).  Right after a kernel that left tens of MB of results in
+  // the L2, a first touch from memory takes some 2 us, and a launch starts with two of them in a row.
+  if (lane == 0 && warp < my_tiles) {
+    constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
+    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
+    int tn, thv, th;
+    split_tile(p, tile, tn, thv, th);
+    long long tslot = 1;
+    if (p.packed) {
+      const int* ip = p.slot_idx + (long long)tn * p.stride_idx;
+      tslot = __ldcg(ip);
+      l2_prefetch_line(reinterpret_cast<const uint8_t*>(p.a) + ((long long)tn * p.stride_a_tok + thv) * (p.ab_dtype == CARRY_F32 ? 4 : 2));
+      l2_prefetch_line(reinterpret_cast<const uint8_t*>(p.b) + ((long long)tn * p.stride_b_tok + thv) * (p.ab_dtype == CARRY_F32 ? 4 : 2));
+    }
+    if (tslot > 0 && (!p.packed || tslot < p.num_slots)) {
+      unsigned long long a[8];
+      tile_addresses<RES, RSCALE, QDT>(p, tn, thv, th, tslot, a);
+#pragma unroll
+      for (int v = D_Q; v <= D_V; ++v) {
+        l2_prefetch_line(reinterpret_cast<const void*>(a[v]));
+        l2_prefetch_line(reinterpret_cast<const void*>(a[v] + kT * qes - 16));
+      }
+      if (warp < 2 * G) {                             // the state of the first two tiles of every group
+        const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
+        const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
+        const long long d_sscale = reinterpret_cast<const uint8_t*>(p.sscale_in) - reinterpret_cast<const uint8_t*>(p.sscale_out);
+        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT);
+        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes);
+        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512);
+      }
+    }
+  }
+  // A rehearsal of the set-up routine on the CTA's first tiles, results discarded (see tile_meta): this code
+  // runs once per launch, and after a launch that streamed 100 MB through the L2 its instructions come
+  // from memory, a microsecond per miss, unless some CTA that got here early has fetched them already.
+  if (warp < my_tiles && warp < G * kWarps)
+    tile_meta<RES, RSCALE, QDT, 32>(p, (int)blockIdx.x + warp * (int)gridDim.x, lane, false, nullptr, nullptr);
+  // nothing before this line consumes global memory or writes it; everything after it sees the results of
+  // the kernels that precede this one in the stream
   asm volatile("griddepcontrol.wait;" ::: "memory");
   // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
   // number % S.  The groups' first tiles are requested before anything else: a request depends on the
