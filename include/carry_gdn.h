@@ -8,7 +8,9 @@
  * memory, never synchronises and never changes the current device: the caller
  * makes the right device current, owns every buffer and keeps it alive until
  * the stream has run the kernel.  Return value: 0 on success, a negative
- * CARRY_GDN_ERR_* otherwise; nothing throws across this boundary.
+ * CARRY_GDN_ERR_* otherwise; nothing throws across this boundary.  Every entry
+ * point reads away the CUDA runtime's per-thread "last error" first, so that a
+ * launch failure it reports is its own.
  *
  * What each entry point replaces in tomalmog/carrykernel (paths relative to
  * that project) is cited above it.
@@ -59,7 +61,8 @@ enum {
 /* bits of the optional device-side status word (OR-ed in by the kernels) */
 enum {
   CARRY_GDN_STATUS_BAD_SLOT = 1,   /* a slot id was >= num_slots; that request was treated as padding */
-  CARRY_GDN_STATUS_TIMEOUT = 2     /* an asynchronous copy did not complete within the wait limit */
+  CARRY_GDN_STATUS_TIMEOUT = 2     /* an asynchronous copy did not complete within the wait limit: that CTA
+                                      stopped loading and storing and left its remaining tiles untouched */
 };
 
 /*
