@@ -546,7 +546,7 @@ def workload_config(args, batch, layers, note=None):
 
 
 # ---------------------------------------------------------------------------
-# the bit-width / granularity sweep (BASELINE config 5)
+# the bit-width / granularity sweep (the bit-width sweep of the named workload configurations (number 5))
 # ---------------------------------------------------------------------------
 
 def config5_sweep(batch=256, steps=512, bits=(3, 4, 5, 6, 8), seed=0):

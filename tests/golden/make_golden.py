@@ -70,7 +70,7 @@ def kernel_test_inputs(T, B, HV, K, V, seed):
 
 
 def config1(rr, rq):
-    """BASELINE config 1 at its stated size: batch 1, 4 heads, K = V = 128, T = 2000 sequential decode
+    """The CPU mechanism configuration (number 1 of the named workloads) at its stated size: batch 1, 4 heads, K = V = 128, T = 2000 sequential decode
     steps, constant decay 0.995, q and k ~ N(0,1) L2-normalised per head, v ~ N(0,1),
     beta = sigmoid(N(0,1)), seed 0, draw order of experiments/exp2b_granularity.py:49-56; int8 state
     with one scale per V column and an fp32 error-feedback residual against the unquantised fp32

@@ -74,7 +74,7 @@ def make_packed_inputs(B, H, HV, K, V, seed, dtype=torch.float32, qk_gain=1.0):
 
 
 def config1_inputs():
-    """BASELINE config 1: batch 1, 4 heads, K = V = 128, T = 2000, constant decay 0.995, q and k
+    """The CPU mechanism configuration (number 1 of the named workloads): batch 1, 4 heads, K = V = 128, T = 2000, constant decay 0.995, q and k
     ~ N(0,1) L2-normalised per head, v ~ N(0,1), beta = sigmoid(N(0,1)), ``torch.manual_seed(0)``,
     drawn in the order of the reference's experiments/exp2b_granularity.py:49-56 (the same draws as
     ``tests/golden/make_golden.py:config1``).  Returns ``(h0, q, k, v, alpha, beta, input_sums)``."""

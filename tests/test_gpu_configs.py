@@ -202,7 +202,7 @@ def test_bit_width_and_decay_sweep():
 
 
 def test_config1_mechanism_full_size_on_the_gpu():
-    """BASELINE config 1 at its stated size through the CUDA entry point: T = 2000 chained steps of
+    """The CPU mechanism configuration (number 1 of the named workloads) at its stated size through the CUDA entry point: T = 2000 chained steps of
     ``gdn_quant_decode_cuda`` (int8 state, one scale per V column, fp32 error-feedback residual) on
     batch 1 x 4 heads x 128 x 128; the final dequantised state against the reference's unquantised fp32
     recurrence (fixture) must show the error the reference's own CPU run of the mechanism shows, within

@@ -108,7 +108,7 @@ def test_mechanism_arms_match_golden():
 
 
 def test_config1_full_size_mechanism_matches_golden():
-    """BASELINE config 1 at its stated size (T = 2000, 4 heads, 128 x 128): the oracle's chain ends in
+    """The CPU mechanism configuration (number 1 of the named workloads) at its stated size (T = 2000, 4 heads, 128 x 128): the oracle's chain ends in
     exactly the states the reference's own code produced, error 6.9e-3 (the reference reports 7.0e-3 for
     its 8-head run of the same recipe)."""
     import parity
