@@ -48,13 +48,18 @@ constexpr int kWarps = 8;
 // Polls of a stage barrier before a wait gives up.  CARRY_TEST_WAIT_EXPIRY builds a test-only library in
 // which the copies of global tile 1 announce 16 bytes more than they bring, so that its barrier never
 // completes, and the limit is short: the expiry path (status bit, poisoned CTA, pool left untouched) then
-// runs in a fraction of a millisecond without anything faulting or hanging.
+// runs in a fraction of a millisecond without anything faulting or hanging.  In the same library the
+// streaming kernel treats the set-up inputs of every tile whose index has bit 1 set as changed under its
+// feet (see the kernel's prologue), so that the path of a launch whose inputs were still being written
+// when it looked at them first runs too -- results must not depend on it.
 #ifdef CARRY_TEST_WAIT_EXPIRY
 constexpr uint32_t kSpinLimit = 1u << 11;
 __device__ __forceinline__ uint32_t test_extra_tx(int tile) { return tile == 1 ? 16u : 0u; }
+__device__ __forceinline__ bool test_inputs_changed(int tile) { return (tile & 2) != 0; }
 #else
 constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ uint32_t test_extra_tx(int) { return 0u; }
+__device__ __forceinline__ bool test_inputs_changed(int) { return false; }
 #endif
 constexpr int kTileCache = 64;         // per group: cached slot ids and gates of the CTA's first tiles
 
@@ -120,6 +125,28 @@ __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* poison, int* status) {
   if (mbar_try_wait(bar, parity)) return true;
   if (!*poison) mbar_wait_slow(bar, parity, poison, status);
+  return !*poison;
+}
+// The wait of the streaming kernel's ring.  A stage holds the tile whose number `*requested` says (written
+// by the thread that requests a tile, before the request): a group that has got ahead of a stalled one
+// reaches tiles nobody has requested yet -- the request for tile n + S is made when tile n is done -- and
+// must not take the stage's previous phase for theirs.  It polls here, within the same limit, instead.
+__device__ __noinline__ void tile_wait_slow(uint64_t* bar, uint32_t parity, const volatile int* requested, int num,
+                                            volatile int* poison, int* status) {
+  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+    if (*requested == num && mbar_try_wait(bar, parity)) return;
+    if (spin > 64) __nanosleep(64);
+    if ((spin & 1023) == 1023 && *poison) return;
+  }
+  *poison = 1;
+  if (status) atomicOr(status, CARRY_GDN_STATUS_TIMEOUT);
+}
+__device__ __forceinline__ bool tile_wait(uint64_t* bar, uint32_t parity, const volatile int* requested, int num,
+                                          volatile int* poison, int* status) {
+  const int req = *requested;                        // both looks are on their way before either is needed
+  const bool landed = mbar_try_wait(bar, parity);
+  if (landed & (req == num)) return true;
+  if (!*poison) tile_wait_slow(bar, parity, requested, num, poison, status);
   return !*poison;
 }
 __device__ __forceinline__ uint4 lds_v4(const void* p) {
@@ -463,7 +490,7 @@ __device__ __forceinline__ void split_tile(const KParams& p, int tile, int& n, i
 
 // What a CTA needs to know about one of its tiles before the data arrives.
 struct __align__(16) TileMeta {
-  int n, hv_h, slot;    // hv_h: value head in the low 16 bits, its key head above them
+  int n, hv, slot;
   float alpha, beta;
   float k_mul, q_mul;   // 1/|k| and scale/|q| (1 when the L2 norm is off or on the statequant path)
   float kq;             // <k, q> after those factors
@@ -510,69 +537,81 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
   }
 }
 
-// Computed by LPT consecutive lanes (4, 8 or 32) straight from global memory: slot id, gates, and the
-// norms of k and q (128 / LPT elements per lane, then a sum over the LPT lanes).  Every load depends on the
-// tile index alone, so the whole thing is one trip to memory however many tiles a CTA prepares at once.  The
-// more lanes share a tile the shorter each lane's instruction stream: a CTA with few tiles (a small batch)
-// gives a whole warp to each, and its first tile can start that much sooner.  The sums are always taken
-// in the same order -- groups of four consecutive elements, then a balanced tree over the groups in index
-// order -- so the result does not depend on LPT (nor on which kernel of this library asks).
-// Every load goes past the L1 (ld.global.cg), which makes the routine safe to run before the kernel's
-// dependency wait with `store` false -- a rehearsal whose results are thrown away: it pulls the
-// routine's instructions and the inputs' lines into the L2, where the real pass then finds them.
-// All 32 lanes of a warp must call this together; when `store` is set, lane 0 of a tile's lanes writes `dst`
-// and lanes 0..3 a quarter of the tile's addresses each to `ddst`.  A slot id beyond the pool is reported in
-// the status word and treated as padding.
-// (tok_*: element offsets of the token within its request, for callers that take several tokens per
-// request; `ddst` may be null.)
-template <int RES, int RSCALE, int QDT, int LPT>
-__device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst,
-                                       long long tok_qkv = 0, long long tok_a = 0, long long tok_b = 0) {
+// A tile's set-up -- slot id, gates, the norms of k and q -- is worked out by LPT consecutive lanes (4, 8 or
+// 32) straight from global memory: 128 / LPT elements of q and k per lane, then sums over the LPT lanes.
+// Every load depends on the tile index alone, so the whole thing is one trip to memory however many tiles
+// a CTA prepares at once.  The more lanes share a tile the shorter each lane's instruction stream: a CTA
+// with few tiles (a small batch) gives a whole warp to each, and its first tile can start that much sooner.
+// The sums are always taken in the same order -- groups of four consecutive elements, then a balanced tree
+// over the groups in index order -- so the result does not depend on LPT (nor on which kernel of this
+// library asks).  The routine comes in pieces -- the loads (meta_load: raw words, all in flight together,
+// past the L1), the arithmetic, a pure function of those words (meta_math, meta_addresses), and the
+// hand-over to shared memory (meta_put) -- because the streaming kernel runs the first two BEFORE its dependency wait,
+// on whatever the inputs hold then, and afterwards only loads the words again: if they have not changed
+// (the rule, since the arithmetic takes a microsecond and the kernel before this one has usually written
+// them long ago) the result stands; if they have, tile_meta() below does it all over.
+template <int QDT, int LPT>
+struct MetaRaw {
   static_assert(LPT == 4 || LPT == 8 || LPT == 32, "lanes per tile");
+  static constexpr int kElems = kT / LPT;                                     // elements per lane and vector
+  static constexpr int kWords = kElems * ((QDT == CARRY_F32) ? 4 : 2) / 4;    // 32-bit words per lane and vector
+  uint32_t qw[kWords], kw[kWords];
+  int slot;
+  GateRaw g;
+};
+template <int QDT, int LPT>
+__device__ __forceinline__ void meta_load(const KParams& p, int n, int hv, int h, int sub, long long tok_qkv,
+                                          long long tok_a, long long tok_b, MetaRaw<QDT, LPT>& r) {
+  using R = MetaRaw<QDT, LPT>;
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
-  constexpr int E = kT / LPT;                          // elements per lane and vector
-  constexpr int kWords = E * qes / 4;                  // 32-bit words per lane and vector
-  constexpr int kGroups4 = E / 4;                      // groups of four elements per lane
-  TileMeta m;
-  int hv, h;
-  split_tile(p, tile, m.n, hv, h);
-  m.hv_h = hv | (h << 16);
   long long q_off, k_off;
   if (p.packed) {
-    q_off = (long long)m.n * p.stride_mixed_tok + (long long)h * kT + tok_qkv;
+    q_off = (long long)n * p.stride_mixed_tok + (long long)h * kT + tok_qkv;
     k_off = q_off + (long long)p.H * kT;
   } else {
-    q_off = k_off = ((long long)m.n * p.HV + hv) * kT;
+    q_off = k_off = ((long long)n * p.HV + hv) * kT;
   }
-  const uint8_t* qp = reinterpret_cast<const uint8_t*>(p.q) + (q_off + E * sub) * qes;
-  const uint8_t* kp = reinterpret_cast<const uint8_t*>(p.k) + (k_off + E * sub) * qes;
-  uint32_t qw[kWords], kw[kWords];
-  if constexpr (kWords >= 4) {
+  const uint8_t* qp = reinterpret_cast<const uint8_t*>(p.q) + (q_off + R::kElems * sub) * qes;
+  const uint8_t* kp = reinterpret_cast<const uint8_t*>(p.k) + (k_off + R::kElems * sub) * qes;
+  if constexpr (R::kWords >= 4) {
 #pragma unroll
-    for (int j = 0; j < kWords / 4; ++j) {
+    for (int j = 0; j < R::kWords / 4; ++j) {
       const uint4 a = __ldcg(reinterpret_cast<const uint4*>(qp) + j), b = __ldcg(reinterpret_cast<const uint4*>(kp) + j);
-      qw[4 * j] = a.x; qw[4 * j + 1] = a.y; qw[4 * j + 2] = a.z; qw[4 * j + 3] = a.w;
-      kw[4 * j] = b.x; kw[4 * j + 1] = b.y; kw[4 * j + 2] = b.z; kw[4 * j + 3] = b.w;
+      r.qw[4 * j] = a.x; r.qw[4 * j + 1] = a.y; r.qw[4 * j + 2] = a.z; r.qw[4 * j + 3] = a.w;
+      r.kw[4 * j] = b.x; r.kw[4 * j + 1] = b.y; r.kw[4 * j + 2] = b.z; r.kw[4 * j + 3] = b.w;
     }
   } else {
-    static_assert(kWords == 2, "a lane's share of a vector is at least 8 bytes");
+    static_assert(R::kWords == 2, "a lane's share of a vector is at least 8 bytes");
     const uint2 a = __ldcg(reinterpret_cast<const uint2*>(qp)), b = __ldcg(reinterpret_cast<const uint2*>(kp));
-    qw[0] = a.x; qw[1] = a.y; kw[0] = b.x; kw[1] = b.y;
+    r.qw[0] = a.x; r.qw[1] = a.y; r.kw[0] = b.x; r.kw[1] = b.y;
   }
-  m.slot = p.packed ? __ldcg(p.slot_idx + (long long)m.n * p.stride_idx) : 1;
-  const GateRaw graw = gate_loads(p, m.n, hv, tok_a, tok_b);      // every load of this routine is in flight now
-  gates_from(p, graw, m.alpha, m.beta);
+  r.slot = p.packed ? __ldcg(p.slot_idx + (long long)n * p.stride_idx) : 1;
+  r.g = gate_loads(p, n, hv, tok_a, tok_b);
+}
+template <int QDT, int LPT>
+__device__ __forceinline__ bool meta_same(const MetaRaw<QDT, LPT>& x, const MetaRaw<QDT, LPT>& y) {
+  uint32_t d = (uint32_t)(x.slot ^ y.slot) | (x.g.a ^ y.g.a) | (x.g.b ^ y.g.b) | (x.g.A_log ^ y.g.A_log) |
+               (x.g.dt_bias ^ y.g.dt_bias);
+#pragma unroll
+  for (int j = 0; j < MetaRaw<QDT, LPT>::kWords; ++j) d |= (x.qw[j] ^ y.qw[j]) | (x.kw[j] ^ y.kw[j]);
+  return d == 0u;
+}
+// fills m.alpha, beta, k_mul, q_mul, kq (all 32 lanes of a warp together: the sums go over lanes)
+template <int QDT, int LPT>
+__device__ __forceinline__ void meta_math(const KParams& p, const MetaRaw<QDT, LPT>& r, TileMeta& m) {
+  constexpr int kGroups4 = MetaRaw<QDT, LPT>::kElems / 4;   // groups of four elements per lane
+  gates_from(p, r.g, m.alpha, m.beta);
   float ks[kGroups4], qs[kGroups4], kq[kGroups4];
 #pragma unroll
   for (int g = 0; g < kGroups4; ++g) {                 // four consecutive elements: one chain each
     float a[4], b[4];
     if (QDT == CARRY_F32) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) { a[c] = __uint_as_float(kw[4 * g + c]); b[c] = __uint_as_float(qw[4 * g + c]); }
+      for (int c = 0; c < 4; ++c) { a[c] = __uint_as_float(r.kw[4 * g + c]); b[c] = __uint_as_float(r.qw[4 * g + c]); }
     } else {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        const float2 ka = act_pair<QDT>(kw[2 * g + c]), qa = act_pair<QDT>(qw[2 * g + c]);
+        const float2 ka = act_pair<QDT>(r.kw[2 * g + c]), qa = act_pair<QDT>(r.qw[2 * g + c]);
         a[2 * c] = ka.x; a[2 * c + 1] = ka.y; b[2 * c] = qa.x; b[2 * c + 1] = qa.y;
       }
     }
@@ -601,18 +640,46 @@ __device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool
     m.q_mul *= p.qscale;
   }
   m.kq = kqsum * (m.k_mul * m.q_mul);
-  if (p.packed && m.slot >= p.num_slots) {
-    if (store && sub == 0 && p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
-    m.slot = 0;
-  }
-  if (store && sub == 0) *dst = m;
-  if (store && ddst && sub < 4) {
-    unsigned long long a[8];
-    tile_addresses<RES, RSCALE, QDT>(p, m.n, hv, h, m.slot > 0 ? m.slot : 0, a);
+}
+// A slot id beyond the pool is treated as padding (and reported by meta_put); the tile's addresses follow
+// from the slot id that is left.  No side effects: this, too, can run ahead of the dependency wait.
+template <int RES, int RSCALE, int QDT>
+__device__ __forceinline__ bool meta_addresses(const KParams& p, TileMeta& m, int hv, int h, unsigned long long (&a)[8]) {
+  const bool bad = p.packed && m.slot >= p.num_slots;
+  if (bad) m.slot = 0;
+  tile_addresses<RES, RSCALE, QDT>(p, m.n, hv, h, m.slot > 0 ? m.slot : 0, a);
+  return bad;
+}
+// Lane 0 of a tile's lanes writes `dst`, lanes 0..3 a quarter of the tile's addresses each to `ddst` (which
+// may be null); a bad slot id goes to the status word.
+__device__ __forceinline__ void meta_put(const KParams& p, const TileMeta& m, const unsigned long long (&a)[8], bool bad,
+                                         int sub, TileMeta* dst, TileDesc* ddst) {
+  if (bad && sub == 0 && p.status) atomicOr(p.status, CARRY_GDN_STATUS_BAD_SLOT);
+  if (sub == 0) *dst = m;
+  if (ddst && sub < 4) {
     const unsigned long long lo = (sub == 0) ? a[0] : (sub == 1) ? a[2] : (sub == 2) ? a[4] : a[6];
     const unsigned long long hi = (sub == 0) ? a[1] : (sub == 1) ? a[3] : (sub == 2) ? a[5] : a[7];
     *reinterpret_cast<ulonglong2*>(&ddst->a[2 * sub]) = make_ulonglong2(lo, hi);
   }
+}
+template <int N> struct LanesPerTile { static constexpr int value = N; };
+// The pieces in a row.  All 32 lanes of a warp must call this together; nothing is written when
+// `store` is false.  (tok_*: element offsets of the token within its request, for callers that take several
+// tokens per request.)
+template <int RES, int RSCALE, int QDT, int LPT>
+__device__ __noinline__ void tile_meta(const KParams& p, int tile, int sub, bool store, TileMeta* dst, TileDesc* ddst,
+                                       long long tok_qkv = 0, long long tok_a = 0, long long tok_b = 0) {
+  TileMeta m;
+  int hv, h;
+  split_tile(p, tile, m.n, hv, h);
+  m.hv = hv;
+  MetaRaw<QDT, LPT> r;
+  meta_load<QDT, LPT>(p, m.n, hv, h, sub, tok_qkv, tok_a, tok_b, r);   // every load of this routine is in flight now
+  m.slot = r.slot;
+  meta_math<QDT, LPT>(p, r, m);
+  unsigned long long a[8];
+  const bool bad = meta_addresses<RES, RSCALE, QDT>(p, m, hv, h, a);
+  if (store) meta_put(p, m, a, bad, sub, dst, ddst);
 }
 
 // Request one tile into the stage at `sb` (called by one thread): the stage barrier's single arrival
@@ -674,12 +741,13 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   __shared__ int claimed[G][2];                      // the tile a group goes on with, by parity of its tile count
   __shared__ int first_cnt[G][2];                    // arrivals at the last meeting of a tile, by the same parity
   __shared__ int poison_flag;
+  __shared__ int stage_tile[S];                      // number of the tile last requested into each stage
   __shared__ float head_red[G][2][kWarps];
   __shared__ TileMeta meta_cache[kCache + G * kWarps];   // this CTA's first tiles; one spare entry per warp
   __shared__ TileDesc desc_cache[kCache + G * kWarps];   // their addresses
   __shared__ __align__(16) float q_warp[(LAYOUT == LAYOUT_VK) ? G * kWarps * kT : 4];   // per warp: q, scaled, as pairs
   __shared__ __align__(16) float col_red_all[(LAYOUT == LAYOUT_KV) ? G * kWarps * kT * 4 : 4];
-  static_assert(sizeof(full_bar) + sizeof(claimed) + sizeof(first_cnt) + sizeof(head_red) + sizeof(meta_cache) + sizeof(desc_cache) +
+  static_assert(sizeof(full_bar) + sizeof(claimed) + sizeof(first_cnt) + sizeof(stage_tile) + sizeof(head_red) + sizeof(meta_cache) + sizeof(desc_cache) +
                         sizeof(q_warp) + sizeof(col_red_all) + 64 <= L::kStatic,
                 "static shared memory exceeds what the stage ring was sized for");
   static_assert(S >= 2 * G, "every group needs a stage in use and one on the way");
@@ -698,95 +766,90 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   if (tid == 0) {
     poison_flag = 0;
     next_seq = G;                                    // tiles 0 .. G-1 are the groups' first ones
-    for (int s = 0; s < S; ++s) mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); stage_tile[s] = -1; }
     for (int g = 0; g < G; ++g) first_cnt[g][0] = first_cnt[g][1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  // While the kernel before this one in the stream finishes, ask the L2 for what this CTA reads first: the
-  // state of its groups' first tiles and the activation rows, gate inputs and slot ids of its first tiles
-  // (one lane per tile).  These are hints only -- nothing is consumed here, and the L2 is where that
-  // kernel's writes land, so whatever it still writes is what the loads below will see.  The slot id that
-  // says where a tile's state lives is read past the L1 for the same reason (it only steers the hints: a
-  // stale or wild one costs a useless prefetch).  Right after a kernel that left tens of MB of results in
-  // the L2, a first touch from memory takes some 2 us, and a launch starts with two of them in a row.
-  if (lane == 0 && warp < my_tiles) {
-    constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
-    const int tile = (int)blockIdx.x + warp * (int)gridDim.x;
-    int tn, thv, th;
-    split_tile(p, tile, tn, thv, th);
-    long long tslot = 1;
-    if (p.packed) {
-      const int* ip = p.slot_idx + (long long)tn * p.stride_idx;
-      tslot = __ldcg(ip);
-      l2_prefetch_line(reinterpret_cast<const uint8_t*>(p.a) + ((long long)tn * p.stride_a_tok + thv) * (p.ab_dtype == CARRY_F32 ? 4 : 2));
-      l2_prefetch_line(reinterpret_cast<const uint8_t*>(p.b) + ((long long)tn * p.stride_b_tok + thv) * (p.ab_dtype == CARRY_F32 ? 4 : 2));
-    }
-    if (tslot > 0 && (!p.packed || tslot < p.num_slots)) {
-      unsigned long long a[8];
-      tile_addresses<RES, RSCALE, QDT>(p, tn, thv, th, tslot, a);
-#pragma unroll
-      for (int v = D_Q; v <= D_V; ++v) {
-        l2_prefetch_line(reinterpret_cast<const void*>(a[v]));
-        l2_prefetch_line(reinterpret_cast<const void*>(a[v] + kT * qes - 16));
-      }
-      if (warp < 2 * G) {                             // the state of the first two tiles of every group
-        const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
-        const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
-        const long long d_sscale = reinterpret_cast<const uint8_t*>(p.sscale_in) - reinterpret_cast<const uint8_t*>(p.sscale_out);
-        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT);
-        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes);
-        l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512);
-      }
-    }
-  }
-  // A rehearsal of the set-up routine on the CTA's first tiles, results discarded (see tile_meta): this code
-  // runs once per launch, and after a launch that streamed 100 MB through the L2 its instructions come
-  // from memory, a microsecond per miss, unless some CTA that got here early has fetched them already.
-  if (warp < my_tiles && warp < G * kWarps)
-    tile_meta<RES, RSCALE, QDT, 32>(p, (int)blockIdx.x + warp * (int)gridDim.x, lane, false, nullptr, nullptr);
-  // nothing before this line consumes global memory or writes it; everything after it sees the results of
-  // the kernels that precede this one in the stream
-  asm volatile("griddepcontrol.wait;" ::: "memory");
   // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
-  // number % S.  The groups' first tiles are requested before anything else: a request depends on the
-  // tile's slot id alone.  Then all threads gather slot ids, gates, norms and addresses of the CTA's first
-  // tiles, four lanes per tile, in one trip to global memory; the rest of the ring is requested after
-  // that, so that the first tiles are not queued behind it.  (Gathering first and requesting the whole
-  // ring afterwards was measured 3 us slower per launch.)
-  // (the last warps make these requests: the first warps are the ones with tiles to prepare when a CTA
-  // has few, and a request worked out from scratch is a long chain of one thread's instructions)
-  if (lane == 0 && warp >= G * kWarps - G && (G * kWarps - 1 - warp) < my_tiles) {
-    const int num = G * kWarps - 1 - warp;
-    const int tile = (int)blockIdx.x + num * (int)gridDim.x;
-    int tn, thv, th;
-    split_tile(p, tile, tn, thv, th);
-    const int tslot = p.packed ? p.slot_idx[(long long)tn * p.stride_idx] : 1;
-    issue_tile<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], tn, thv, th, tslot);
-  }
-  __syncwarp();
-  {
-    // lanes per tile: as many as the CTA's tile count leaves room for in one pass over its threads
-    static_assert(kThreads / 4 == kTileCache, "at four lanes per tile one pass covers the whole cache");
-    const int cached = my_tiles < kCache ? my_tiles : kCache;
-    if (cached <= G * kWarps) {                      // a warp per tile
-      if (warp < cached)
-        tile_meta<RES, RSCALE, QDT, 32>(p, (int)blockIdx.x + warp * (int)gridDim.x, lane, true, &meta_cache[warp],
-                                        &desc_cache[warp]);
-    } else if (cached <= G * kWarps * 4) {           // eight lanes per tile
-      const int i = tid >> 3;
-      const bool valid = i < cached;
-      if (warp * 4 < cached)
-        tile_meta<RES, RSCALE, QDT, 8>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 7, valid,
-                                       &meta_cache[i], &desc_cache[i]);
-    } else {                                         // four lanes per tile
-      const int i = tid >> 2;
-      const bool valid = i < cached;
-      if (warp * 8 < cached)                         // warps without a tile to prepare stay out of the way
-        tile_meta<RES, RSCALE, QDT, 4>(p, (int)blockIdx.x + (valid ? i : 0) * (int)gridDim.x, tid & 3, valid,
-                                       &meta_cache[i], &desc_cache[i]);
+  // number % S.  Set-up of the first ones (up to the cache's size), by all threads at 32, 8 or 4 lanes per
+  // tile -- as many as the tile count leaves room for in one pass -- in two halves around the dependency
+  // wait:
+  //   before it, while the kernel ahead in the stream finishes: load the tiles' inputs past the L1, work
+  //     out slot id, gates and norms from whatever they hold, keep both in registers; hint the L2 at the
+  //     state of the groups' first tiles and at the v rows.  Nothing here writes memory or hands a value on.
+  //   after it: the same loads again, now ordered after every write of that kernel.  Equal words mean the
+  //     figures worked out beforehand are the ones this launch must use: the groups' first tiles are
+  //     requested at once, from the addresses already in registers (the rest of the ring only after all
+  //     threads have met, so that the first tiles are not queued behind it), and the figures go to the
+  //     cache.  A warp that sees a difference runs the whole routine again.
+  // Right after a kernel that left tens of MB of results in the L2 a first touch of memory takes some 2 us
+  // and the routine's arithmetic, fetched cold, another microsecond: this way both pass while the CTA would
+  // otherwise sit in the wait, and what is left behind it is one trip to the L2.
+  const int cached = my_tiles < kCache ? my_tiles : kCache;
+  auto setup = [&](auto lanes_per_tile) {
+    constexpr int LPT = decltype(lanes_per_tile)::value;
+    constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
+    const int num = (LPT == 32) ? warp : (LPT == 8) ? (tid >> 3) : (tid >> 2);   // the tile these lanes prepare
+    const int sub = (LPT == 32) ? lane : (LPT == 8) ? (tid & 7) : (tid & 3);
+    const bool valid = num < cached;
+    const bool busy = warp * (32 / LPT) < cached;        // warps without a tile to prepare stay out of the way
+    const int tile = (int)blockIdx.x + (valid ? num : 0) * (int)gridDim.x;
+    const int entry = valid ? num : 0;
+    TileMeta m;
+    MetaRaw<QDT, LPT> before;
+    unsigned long long a[8];
+    bool bad = false;
+    int hv = 0, h = 0;
+    if (busy) {
+      split_tile(p, tile, m.n, hv, h);
+      m.hv = hv;
+      meta_load<QDT, LPT>(p, m.n, hv, h, sub, 0, 0, 0, before);
+      m.slot = before.slot;
+      bad = meta_addresses<RES, RSCALE, QDT>(p, m, hv, h, a);
+      if (sub == 0 && valid && m.slot > 0) {
+        l2_prefetch_line(reinterpret_cast<const void*>(a[D_V]));
+        l2_prefetch_line(reinterpret_cast<const void*>(a[D_V] + kT * qes - 16));
+        if (num < 2 * G) {                               // the state of the first two tiles of every group
+          const long long d_codes = reinterpret_cast<const uint8_t*>(p.codes_in) - reinterpret_cast<const uint8_t*>(p.codes_out);
+          const long long d_resid = reinterpret_cast<const uint8_t*>(p.resid_in) - reinterpret_cast<const uint8_t*>(p.resid_out);
+          const long long d_sscale = reinterpret_cast<const uint8_t*>(p.sscale_in) - reinterpret_cast<const uint8_t*>(p.sscale_out);
+          l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_CODES] + d_codes), kT * kT);
+          l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_RESID] + d_resid), L::kResidBytes);
+          l2_prefetch_bulk(reinterpret_cast<const void*>(a[D_SSCALE] + d_sscale), 512);
+        }
+      }
+      meta_math<QDT, LPT>(p, before, m);
     }
-  }
+    // nothing before this line hands on what it read from global memory, or writes it; everything after it
+    // sees the results of the kernels that precede this one in the stream
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (busy) {
+      MetaRaw<QDT, LPT> now;
+      meta_load<QDT, LPT>(p, m.n, hv, h, sub, 0, 0, 0, now);
+      const bool first = valid && sub == 0 && num < G;   // the lane that requests a group's first tile
+      if (__all_sync(0xffffffffu, meta_same<QDT, LPT>(before, now) && !test_inputs_changed(tile))) {
+        if (first) {
+          *reinterpret_cast<volatile int*>(&stage_tile[num]) = num;
+          if (m.slot <= 0) mbar_arrive(&full_bar[num]);
+          else issue_copies<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], a, tile);
+        }
+        if (valid) meta_put(p, m, a, bad, sub, &meta_cache[entry], &desc_cache[entry]);
+      } else {
+        tile_meta<RES, RSCALE, QDT, LPT>(p, tile, sub, valid, &meta_cache[entry], &desc_cache[entry]);
+        __syncwarp();
+        if (first) {
+          *reinterpret_cast<volatile int*>(&stage_tile[num]) = num;
+          issue_cached<LAYOUT, RES, RSCALE, QDT>(p, smem + (size_t)num * L::kBytes, &full_bar[num], &desc_cache[num],
+                                                 meta_cache[num].slot, tile);
+        }
+      }
+    }
+  };
+  static_assert(kThreads / 4 == kTileCache, "at four lanes per tile one pass covers the whole cache");
+  if (cached <= G * kWarps) setup(LanesPerTile<32>{});
+  else if (cached <= G * kWarps * 4) setup(LanesPerTile<8>{});
+  else setup(LanesPerTile<4>{});
   __syncthreads();
   static_assert(S <= G * kWarps && S <= kTileCache, "one warp per stage issues the first requests, from the cache");
 
@@ -794,6 +857,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
   auto load_tile = [&](int num) {                   // one thread requests tile `num`
     uint8_t* dst_stage = smem + (size_t)(num % S) * L::kBytes;
+    *reinterpret_cast<volatile int*>(&stage_tile[num % S]) = num;
     if (num < kCache) {
       issue_cached<LAYOUT, RES, RSCALE, QDT>(p, dst_stage, &full_bar[num % S], &desc_cache[num], meta_cache[num].slot,
                                              (int)blockIdx.x + num * (int)gridDim.x);
@@ -836,9 +900,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
       __syncwarp();
     }
     const uint4 tm0 = lds_v4(tm);
-    const int n = (int)tm0.x, hv = (int)(tm0.y & 0xffffu);
+    const int n = (int)tm0.x, hv = (int)tm0.y;
 
-    const bool healthy = mbar_wait(&full_bar[s], parity, poison, p.status);
+    const bool healthy = tile_wait(&full_bar[s], parity, &stage_tile[s], it, poison, p.status);
     const int slot = (int)tm0.z;
     const int out_row = n * p.HV + hv;                // outputs of this tile start at element out_row * 128
     const bool live = slot > 0 && healthy;

@@ -8,6 +8,12 @@ announce 16 bytes more than they bring, so that tile's stage barrier can never
 complete, and the poll limit is short.  Expected of every kernel: the launch
 returns, the status bit is set, the tile's state and output are exactly as they
 were, and every other tile equals what the regular library computes.
+
+The twin also makes the streaming kernel take, for every tile whose index has
+bit 1 set, the path of a launch whose set-up inputs changed between its look at
+them ahead of the stream dependency and its second look after it (the whole
+set-up is then done again): "every other tile equals what the regular library
+computes" therefore covers that path as well, bit for bit.
 """
 
 from __future__ import annotations
@@ -88,6 +94,50 @@ def test_single_token_kernel_wait_runs_out(resid_fmt, rscale):
     status.zero_()
     run([x.clone() for x in st], status)
     assert int(status.item()) == 0
+
+
+@pytest.mark.parametrize("B", [4, 160, 400])       # 1, 35 and 87 tiles per CTA: 32, 8 and 4 lanes per tile in the set-up
+def test_set_up_done_again_gives_the_same_results(B):
+    """Tiles whose set-up the twin does twice (index bit 1 set) against the regular library, bit for bit.
+
+    The CTA that owns global tile 1 stops at that tile (its wait runs out), so all of that CTA's tiles
+    are left out of the comparison."""
+    from carrykernel_b200 import _lib
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    H = HV = 32
+    K = V = 128
+    num_slots = B + 2
+    g = torch.Generator().manual_seed(5)
+    st = [x.to(DEV) for x in qpd.init_quantized_state(num_slots, HV, V, K, "cpu", resid_fmt=1, resid_scale="head")]
+    st[0].copy_(torch.randint(-127, 128, st[0].shape, generator=g, dtype=torch.int8))
+    st[1].copy_(torch.rand(st[1].shape, generator=g) * 1e-3 + 1e-4)
+    idx = (torch.randperm(num_slots - 1, generator=g)[:B] + 1).to(torch.int32).to(DEV)
+    mixed, a, b, A_log, dt_bias = [x.to(DEV) for x in make_packed_inputs(B, H, HV, K, V, seed=11, dtype=torch.bfloat16)]
+    A_log, dt_bias = A_log.float(), dt_bias.float()
+
+    def run(pool, status):
+        out = torch.full((B, 1, HV, V), float("nan"), dtype=torch.bfloat16, device=DEV)
+        qpd.quantized_gated_delta_rule_packed_decode(mixed, a, b, A_log, dt_bias, K ** -0.5, *pool, out, idx,
+                                                     use_qk_l2norm_in_kernel=True, resid_fmt=1, status=status)
+        torch.cuda.synchronize()
+        return out
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    good = [x.clone() for x in st]
+    out_good = run(good, status)
+    assert int(status.item()) == 0
+    twin = [x.clone() for x in st]
+    with wait_test_library():
+        out_twin = run(twin, status)
+    assert int(status.item()) == _lib.STATUS_TIMEOUT
+    ctas = torch.cuda.get_device_properties(0).multi_processor_count
+    tile = torch.arange(B * HV, device=DEV).view(B, HV)
+    keep = (tile % ctas) != 1
+    assert int((keep & ((tile & 2) != 0)).sum()) > 0
+    assert torch.equal(out_twin[:, 0][keep].float(), out_good[:, 0][keep].float())
+    rows = idx.long()
+    for x_twin, x_good in zip(twin, good):
+        assert torch.equal(x_twin[rows][keep], x_good[rows][keep])
 
 
 def test_multi_token_kernel_wait_runs_out():
