@@ -548,8 +548,8 @@ __device__ __forceinline__ void tile_addresses(const KParams& p, int n, int hv, 
 // past the L1), the arithmetic, a pure function of those words (meta_math, meta_addresses), and the
 // hand-over to shared memory (meta_put) -- because the streaming kernel runs the first two BEFORE its dependency wait,
 // on whatever the inputs hold then, and afterwards only loads the words again: if they have not changed
-// (the rule, since the arithmetic takes a microsecond and the kernel before this one has usually written
-// them long ago) the result stands; if they have, tile_meta() below does it all over.
+// (meta_unchanged; the rule, since the arithmetic takes a microsecond and the kernel before this one has
+// usually written them long ago) the result stands; if they have, tile_meta() below does it all over.
 template <int QDT, int LPT>
 struct MetaRaw {
   static_assert(LPT == 4 || LPT == 8 || LPT == 32, "lanes per tile");
@@ -559,10 +559,10 @@ struct MetaRaw {
   int slot;
   GateRaw g;
 };
+// where a lane's share of q and k starts
 template <int QDT, int LPT>
-__device__ __forceinline__ void meta_load(const KParams& p, int n, int hv, int h, int sub, long long tok_qkv,
-                                          long long tok_a, long long tok_b, MetaRaw<QDT, LPT>& r) {
-  using R = MetaRaw<QDT, LPT>;
+__device__ __forceinline__ void meta_vectors(const KParams& p, int n, int hv, int h, int sub, long long tok_qkv,
+                                             const uint8_t*& qp, const uint8_t*& kp) {
   constexpr int qes = (QDT == CARRY_F32) ? 4 : 2;
   long long q_off, k_off;
   if (p.packed) {
@@ -571,8 +571,15 @@ __device__ __forceinline__ void meta_load(const KParams& p, int n, int hv, int h
   } else {
     q_off = k_off = ((long long)n * p.HV + hv) * kT;
   }
-  const uint8_t* qp = reinterpret_cast<const uint8_t*>(p.q) + (q_off + R::kElems * sub) * qes;
-  const uint8_t* kp = reinterpret_cast<const uint8_t*>(p.k) + (k_off + R::kElems * sub) * qes;
+  qp = reinterpret_cast<const uint8_t*>(p.q) + (q_off + MetaRaw<QDT, LPT>::kElems * sub) * qes;
+  kp = reinterpret_cast<const uint8_t*>(p.k) + (k_off + MetaRaw<QDT, LPT>::kElems * sub) * qes;
+}
+template <int QDT, int LPT>
+__device__ __forceinline__ void meta_load(const KParams& p, int n, int hv, int h, int sub, long long tok_qkv,
+                                          long long tok_a, long long tok_b, MetaRaw<QDT, LPT>& r) {
+  using R = MetaRaw<QDT, LPT>;
+  const uint8_t *qp, *kp;
+  meta_vectors<QDT, LPT>(p, n, hv, h, sub, tok_qkv, qp, kp);
   if constexpr (R::kWords >= 4) {
 #pragma unroll
     for (int j = 0; j < R::kWords / 4; ++j) {
@@ -588,12 +595,41 @@ __device__ __forceinline__ void meta_load(const KParams& p, int n, int hv, int h
   r.slot = p.packed ? __ldcg(p.slot_idx + (long long)n * p.stride_idx) : 1;
   r.g = gate_loads(p, n, hv, tok_a, tok_b);
 }
+// The same loads again, compared with `x` as they come in: true when no word differs.  At most four 16-byte
+// loads per vector are in flight at a time, so that the second look needs no second set of registers for
+// the 32 words per vector of fp32 activations at four lanes per tile.
 template <int QDT, int LPT>
-__device__ __forceinline__ bool meta_same(const MetaRaw<QDT, LPT>& x, const MetaRaw<QDT, LPT>& y) {
-  uint32_t d = (uint32_t)(x.slot ^ y.slot) | (x.g.a ^ y.g.a) | (x.g.b ^ y.g.b) | (x.g.A_log ^ y.g.A_log) |
-               (x.g.dt_bias ^ y.g.dt_bias);
+__device__ __forceinline__ bool meta_unchanged(const KParams& p, int n, int hv, int h, int sub,
+                                               const MetaRaw<QDT, LPT>& x) {
+  using R = MetaRaw<QDT, LPT>;
+  const uint8_t *qp, *kp;
+  meta_vectors<QDT, LPT>(p, n, hv, h, sub, 0, qp, kp);
+  const int slot = p.packed ? __ldcg(p.slot_idx + (long long)n * p.stride_idx) : 1;
+  const GateRaw g = gate_loads(p, n, hv, 0, 0);
+  uint32_t d = 0u;
+  if constexpr (R::kWords >= 4) {
+    constexpr int kQuads = R::kWords / 4, kBatch = kQuads < 4 ? kQuads : 4;
 #pragma unroll
-  for (int j = 0; j < MetaRaw<QDT, LPT>::kWords; ++j) d |= (x.qw[j] ^ y.qw[j]) | (x.kw[j] ^ y.kw[j]);
+    for (int j0 = 0; j0 < kQuads; j0 += kBatch) {
+      uint4 a[kBatch], b[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        a[j] = __ldcg(reinterpret_cast<const uint4*>(qp) + j0 + j);
+        b[j] = __ldcg(reinterpret_cast<const uint4*>(kp) + j0 + j);
+      }
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const int w = 4 * (j0 + j);
+        d |= (a[j].x ^ x.qw[w]) | (a[j].y ^ x.qw[w + 1]) | (a[j].z ^ x.qw[w + 2]) | (a[j].w ^ x.qw[w + 3]);
+        d |= (b[j].x ^ x.kw[w]) | (b[j].y ^ x.kw[w + 1]) | (b[j].z ^ x.kw[w + 2]) | (b[j].w ^ x.kw[w + 3]);
+      }
+      if (j0 + kBatch < kQuads) asm volatile("" ::: "memory");   // the next batch's loads stay behind this one's use
+    }
+  } else {
+    const uint2 a = __ldcg(reinterpret_cast<const uint2*>(qp)), b = __ldcg(reinterpret_cast<const uint2*>(kp));
+    d = (a.x ^ x.qw[0]) | (a.y ^ x.qw[1]) | (b.x ^ x.kw[0]) | (b.y ^ x.kw[1]);
+  }
+  d |= (uint32_t)(slot ^ x.slot) | (g.a ^ x.g.a) | (g.b ^ x.g.b) | (g.A_log ^ x.g.A_log) | (g.dt_bias ^ x.g.dt_bias);
   return d == 0u;
 }
 // fills m.alpha, beta, k_mul, q_mul, kq (all 32 lanes of a warp together: the sums go over lanes)
@@ -825,10 +861,9 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     // sees the results of the kernels that precede this one in the stream
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (busy) {
-      MetaRaw<QDT, LPT> now;
-      meta_load<QDT, LPT>(p, m.n, hv, h, sub, 0, 0, 0, now);
+      const bool same = meta_unchanged<QDT, LPT>(p, m.n, hv, h, sub, before);
       const bool first = valid && sub == 0 && num < G;   // the lane that requests a group's first tile
-      if (__all_sync(0xffffffffu, meta_same<QDT, LPT>(before, now) && !test_inputs_changed(tile))) {
+      if (__all_sync(0xffffffffu, same && !test_inputs_changed(tile))) {
         if (first) {
           *reinterpret_cast<volatile int*>(&stage_tile[num]) = num;
           if (m.slot <= 0) mbar_arrive(&full_bar[num]);
