@@ -68,7 +68,7 @@ assert TILE_BYTES == 51216 and SLOT_LAYER_BYTES == 1638916
 # of the results is inside the window), keyed by the SHA-256 of the kernel sources the profiled library
 # was built from.  A library built from other sources gets null until it has been profiled again.
 NCU_TRAFFIC_BY_SOURCE = {
-    "a207bb0993ac1b8e": 103_810_000,
+    "8b0c3b80b1913f77": 103_760_000,
 }
 KERNEL_SOURCES = ("carry_gdn_tile128.cuh", "carry_gdn_slot_tile.inc", "carry_gdn_common.cuh")
 
@@ -308,7 +308,7 @@ def time_graph(graph, steps, device):
     return start.elapsed_time(end) * 1e-3
 
 
-def e2e_run(wl, steps, warmup, groups, kernels=True):
+def e2e_run(wl, steps, warmup, groups, kernels=True, repeats=1):
     """The same step through the public call with HOST buffers.  Every step copies all activations and
     slot ids from pinned host memory to the device, runs the 24 layer calls, and copies every output
     row back to pinned host memory; the step ends when the host holds all outputs (stream
@@ -359,13 +359,15 @@ def e2e_run(wl, steps, warmup, groups, kernels=True):
 
     for _ in range(warmup):
         one_step()
-    torch.cuda.synchronize(dev)
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one_step()
-    torch.cuda.synchronize(dev)
-    wall = time.perf_counter() - t0
-    return wall, wl.in_bytes_useful, wl.out_bytes_useful
+    walls = []
+    for _ in range(max(1, repeats)):                    # the region of `steps` steps, several times: the median
+        torch.cuda.synchronize(dev)                     # keeps one hiccup of a shared host out of the figure
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            one_step()
+        torch.cuda.synchronize(dev)
+        walls.append(time.perf_counter() - t0)
+    return median(walls), wl.in_bytes_useful, wl.out_bytes_useful
 
 
 # ---------------------------------------------------------------------------
@@ -1077,15 +1079,17 @@ def main():
         from carrykernel_b200.sharding import max_over_ranks
         # the copies-only replay is taken before and after the real one and the smaller kept: the host's
         # copy rate wanders by some 20 % between one second and the next on a shared machine
-        t_floor0, _, _ = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, kernels=False)
-        t_e2e, h2d, d2h = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups)
+        rep = max(1, args.repeats)
+        t_floor0, _, _ = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, kernels=False, repeats=rep)
+        t_e2e, h2d, d2h = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, repeats=rep)
         t_e2e = max_over_ranks(t_e2e, device)
-        t_floor1, _, _ = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, kernels=False)
+        t_floor1, _, _ = e2e_run(wl, args.steps, max(args.warmup, 3), groups=args.e2e_groups, kernels=False, repeats=rep)
         t_floor = min(max_over_ranks(t_floor0, device), max_over_ranks(t_floor1, device))
         e2e = {"value": units_per_step * args.steps / t_e2e, "unit": UNIT,
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                "ms_per_step": t_e2e / args.steps * 1e3,
-               "copy_floor_ms_per_step": t_floor / args.steps * 1e3}
+               "copy_floor_ms_per_step": t_floor / args.steps * 1e3,
+               "timed_regions": rep}                     # each of `steps` steps; the median region is reported
 
     sweep = strong_pt = c5 = None
     if not args.no_extras and not strong:

@@ -52,6 +52,7 @@ int packed_params(const CarryGdnPackedArgs* a, KParams& p) {
   p.packed = 1;
   p.B = a->B; p.H = a->H; p.HV = a->HV; p.K = a->K; p.V = a->V;
   p.qmax = a->qmax;
+  p.inv_qmax = 1.0f / a->qmax;
   p.res_fmt = a->res_fmt; p.rscale_mode = a->resid_scale_mode; p.sscale_mode = CARRY_SCALE_PER_V;
   p.eps_mode = a->eps_mode;
   p.qkv_dtype = a->qkv_dtype; p.o_dtype = a->out_dtype;
@@ -125,6 +126,7 @@ int carry_gdn_quant_step(const CarryGdnStepArgs* a, void* stream) {
   p.packed = 0;
   p.B = a->B; p.H = a->HV; p.HV = a->HV; p.K = a->K; p.V = a->V;
   p.qmax = a->qmax;
+  p.inv_qmax = 1.0f / a->qmax;
   p.res_fmt = a->res_fmt; p.rscale_mode = a->resid_scale_mode; p.sscale_mode = a->state_scale_mode;
   p.eps_mode = a->eps_mode;
   p.qkv_dtype = a->qkv_dtype; p.o_dtype = a->o_dtype;

@@ -25,6 +25,7 @@ struct KParams {
   int group;         // value heads per key head, HV / H                    the streaming kernel splits tile
   int group_shift;   // log2(group) when that is a power of two, else -1    indices without dividing)
   float qmax;
+  float inv_qmax;    // 1 / qmax rounded to nearest, worked out on the host (the streaming kernels multiply by it)
   int res_fmt, rscale_mode, sscale_mode, eps_mode;
   int qkv_dtype, o_dtype;
   int* status;

@@ -76,8 +76,9 @@ __global__ void __launch_bounds__(kThreads, 2) gdn_multi_kernel(const __grid_con
     bulk_load(sb + L::kSScale, reinterpret_cast<const void*>(a8[D_SSCALE]), 512, &full_bar);
     bulk_load(sb + L::kRScale, reinterpret_cast<const void*>(a8[D_RSCALE_IN]), L::kRScaleBytes, &full_bar);
   }
-  const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
-  const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);
+  constexpr float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
+  constexpr float rrqmax = 1.0f / rqmax;             // rounded to nearest, like the host's p.inv_qmax
+  const float rqmax_state = p.inv_qmax;
   bool healthy = true;
 
   for (int t = 0; t < x.T; ++t) {

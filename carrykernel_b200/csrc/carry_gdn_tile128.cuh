@@ -888,8 +888,12 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
   __syncthreads();
   static_assert(S <= G * kWarps && S <= kTileCache, "one warp per stage issues the first requests, from the cache");
 
-  const float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
-  const float rrqmax = __frcp_rn(rqmax), rqmax_state = __frcp_rn(p.qmax);   // correctly rounded: div_qmax relies on it
+  // reciprocals rounded to nearest (div_qmax relies on it): a constant, and one that the host worked out --
+  // the correctly rounded device routine is a subroutine call that, fetched cold right after the wait, was
+  // seen to take up to a microsecond
+  constexpr float rqmax = (RES == CARRY_RES_INT4) ? 7.0f : 127.0f;
+  constexpr float rrqmax = 1.0f / rqmax;
+  const float rqmax_state = p.inv_qmax;
   auto load_tile = [&](int num) {                   // one thread requests tile `num`
     uint8_t* dst_stage = smem + (size_t)(num % S) * L::kBytes;
     *reinterpret_cast<volatile int*>(&stage_tile[num % S]) = num;
