@@ -56,10 +56,17 @@ constexpr int kWarps = 8;
 constexpr uint32_t kSpinLimit = 1u << 11;
 __device__ __forceinline__ uint32_t test_extra_tx(int tile) { return tile == 1 ? 16u : 0u; }
 __device__ __forceinline__ bool test_inputs_changed(int tile) { return (tile & 2) != 0; }
+// ... and reports, in a status bit of its own, when a tile's inputs really had changed between the two looks
+// (tests/test_gpu_wait_expiry.py provokes that with a kernel that writes them late)
+constexpr int kTestStatusInputsChanged = 1 << 30;
+__device__ __forceinline__ void test_note_changed(int* status, bool same) {
+  if (!same && status) atomicOr(status, kTestStatusInputsChanged);
+}
 #else
 constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ uint32_t test_extra_tx(int) { return 0u; }
 __device__ __forceinline__ bool test_inputs_changed(int) { return false; }
+__device__ __forceinline__ void test_note_changed(int*, bool) {}
 #endif
 constexpr int kTileCache = 64;         // per group: cached slot ids and gates of the CTA's first tiles
 
@@ -862,6 +869,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (busy) {
       const bool same = meta_unchanged<QDT, LPT>(p, m.n, hv, h, sub, before);
+      test_note_changed(p.status, same);
       const bool first = valid && sub == 0 && num < G;   // the lane that requests a group's first tile
       if (__all_sync(0xffffffffu, same && !test_inputs_changed(tile))) {
         if (first) {

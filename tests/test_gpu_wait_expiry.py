@@ -140,6 +140,71 @@ def test_set_up_done_again_gives_the_same_results(B):
         assert torch.equal(x_twin[rows][keep], x_good[rows][keep])
 
 
+def test_inputs_written_late_by_the_kernel_ahead():
+    """A real change of the inputs between the streaming kernel's two looks at them.
+
+    The twin library has a kernel that lets its successor start at once, idles 50 us and only then writes
+    the activations.  The decode call queued right behind it takes its first look while the buffer still
+    holds other values, finds them changed after its dependency wait (the twin reports that in a status bit
+    of its own) and must redo its set-up: results equal the regular library's on the final inputs."""
+    import ctypes as C
+    from carrykernel_b200 import _lib
+    from carrykernel_b200.vllm_integration import quantized_packed_decode as qpd
+    B, H, HV, K, V = 16, 32, 32, 128, 128
+    num_slots = B + 2
+    g = torch.Generator().manual_seed(8)
+    pool = torch.randn(num_slots, HV, V, K, generator=g) * 0.1
+    st = [x.to(DEV) for x in qpd.init_quantized_state(num_slots, HV, V, K, "cpu", h0=pool, resid_fmt=1, resid_scale="head")]
+    idx = (torch.randperm(num_slots - 1, generator=g)[:B] + 1).to(torch.int32).to(DEV)
+    mixed, a, b, A_log, dt_bias = [x.to(DEV) for x in make_packed_inputs(B, H, HV, K, V, seed=12, dtype=torch.bfloat16)]
+    early = make_packed_inputs(B, H, HV, K, V, seed=13, dtype=torch.bfloat16)[0].to(DEV)   # what the buffer holds first
+    A_log, dt_bias = A_log.float(), dt_bias.float()
+
+    def run(pool_, status, mixed_, out):
+        qpd.quantized_gated_delta_rule_packed_decode(mixed_, a, b, A_log, dt_bias, K ** -0.5, *pool_, out, idx,
+                                                     use_qk_l2norm_in_kernel=True, resid_fmt=1, status=status)
+
+    def fresh_out():
+        return torch.full((B, 1, HV, V), float("nan"), dtype=torch.bfloat16, device=DEV)
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    good, out_good = [x.clone() for x in st], fresh_out()
+    run(good, status, mixed, out_good)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    twin, out_twin, buf = [x.clone() for x in st], fresh_out(), early.clone()
+    side = torch.cuda.Stream(DEV)
+    with wait_test_library():
+        lib = _lib.load_library()
+        lib.carry_gdn_test_late_writer.argtypes = [C.c_void_p, C.c_void_p, C.c_longlong, C.c_uint, C.c_void_p]
+        lib.carry_gdn_test_late_writer.restype = C.c_int
+        with torch.cuda.stream(side):                 # once outside a graph: first-call set-up of the twin
+            run([x.clone() for x in st], torch.zeros(1, dtype=torch.int32, device=DEV), mixed, fresh_out())
+        torch.cuda.synchronize()
+        # writer and decode call as neighbours in one graph: no host time between the two launches
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            rc = lib.carry_gdn_test_late_writer(buf.data_ptr(), mixed.data_ptr(), buf.numel() * buf.element_size(), 50000,
+                                                torch.cuda.current_stream().cuda_stream)
+            run(twin, status, buf, out_twin)
+        assert rc == 0
+        status.zero_()
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+    code = int(status.item())
+    assert code & (1 << 30), "the decode call never saw its inputs change: the race this test is about did not happen"
+    assert code & ~(1 << 30) == _lib.STATUS_TIMEOUT      # the twin's sabotaged tile 1, as in every run of it
+    assert torch.equal(buf, mixed)
+    ctas = torch.cuda.get_device_properties(0).multi_processor_count
+    tile = torch.arange(B * HV, device=DEV).view(B, HV)
+    keep = (tile % ctas) != 1
+    assert torch.equal(out_twin[:, 0][keep].float(), out_good[:, 0][keep].float())
+    rows = idx.long()
+    for x_twin, x_good in zip(twin, good):
+        assert torch.equal(x_twin[rows][keep], x_good[rows][keep])
+
+
 def test_multi_token_kernel_wait_runs_out():
     from carrykernel_b200 import _lib
     qpd, (B, H, HV, K, V), st, idx = _slot_case(1, "head")
