@@ -18,8 +18,9 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libcarry_gdn.so")
 # Test-only twin of the library, built with CARRY_TEST_WAIT_EXPIRY: one tile's copies never complete and the
-# wait limit is short, so that tests/test_gpu_wait_expiry.py can watch a bounded wait run out.  Nothing
-# in the package loads it.
+# wait limit is short, so that tests/test_gpu_wait_expiry.py can watch a bounded wait run out; it also
+# forces, reports and (with an extra kernel that writes a buffer late) provokes the path of set-up inputs
+# that changed under the streaming kernel's feet.  Nothing in the package loads it.
 WAIT_TEST_LIB = os.path.join(PKG, "libcarry_gdn_waittest.so")
 SOURCES = ("carry_gdn_api.cu", "carry_gdn_generic.cu", "carry_gdn_tile128.cu",
            "carry_gdn_tile128_vk.cu", "carry_gdn_tile128_kv.cu", "carry_gdn_multi.cu",

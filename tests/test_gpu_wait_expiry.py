@@ -13,7 +13,11 @@ The twin also makes the streaming kernel take, for every tile whose index has
 bit 1 set, the path of a launch whose set-up inputs changed between its look at
 them ahead of the stream dependency and its second look after it (the whole
 set-up is then done again): "every other tile equals what the regular library
-computes" therefore covers that path as well, bit for bit.
+computes" therefore covers that path as well, bit for bit.  For a change that
+is real, the twin also exports ``carry_gdn_test_late_writer`` -- a kernel that
+lets the launch behind it start, idles, and only then copies a buffer -- and
+ORs bit 30 into the status word when a tile's inputs differed between the
+two looks.
 """
 
 from __future__ import annotations
