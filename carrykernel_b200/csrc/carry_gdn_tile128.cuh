@@ -806,14 +806,16 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
 
   // let the next kernel in the stream, if it asked for it, move in behind this one (see launch_variant)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-  if (tid == 0) {
+  // the CTA's bookkeeping is set up by its last thread (the last warp is the one least likely to have a tile
+  // to prepare) and published by the meeting right before the dependency wait: nothing ahead of that
+  // meeting touches it, so the set-up's loads are on their way first
+  if (tid == G * kThreads - 1) {
     poison_flag = 0;
     next_seq = G;                                    // tiles 0 .. G-1 are the groups' first ones
     for (int s = 0; s < S; ++s) { mbar_init(&full_bar[s], 1); stage_tile[s] = -1; }
     for (int g = 0; g < G; ++g) first_cnt[g][0] = first_cnt[g][1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  __syncthreads();
   // Tiles of this CTA are numbered 0, 1, 2, ... (tile = blockIdx.x + number * gridDim.x) and sit in stage
   // number % S.  Set-up of the first ones (up to the cache's size), by all threads at 32, 8 or 4 lanes per
   // tile -- as many as the tile count leaves room for in one pass -- in two halves around the dependency
@@ -866,6 +868,7 @@ gdn_tile128_kernel(const __grid_constant__ KParams p) {
     }
     // nothing before this line hands on what it read from global memory, or writes it; everything after it
     // sees the results of the kernels that precede this one in the stream
+    __syncthreads();
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (busy) {
       const bool same = meta_unchanged<QDT, LPT>(p, m.n, hv, h, sub, before);
